@@ -1,0 +1,112 @@
+/*
+ * ramnet_b200 -- C ABI of the B200 (sm_100a) kernels for RAM-Net's sparse slot-memory path.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides.  The library
+ * never allocates, frees or synchronises: the caller owns inputs, outputs and workspaces and
+ * passes the CUDA stream to launch on (as a cudaStream_t cast to void*).  Return value 0 means
+ * the launch was enqueued; non-zero means nothing was launched and rn_last_error() describes
+ * why (thread-local text).  Citations name the reference interface each entry point replaces,
+ * by path inside the reference project.
+ *
+ * Symbols: B batch, T tokens, H heads, U address digits, P radix, A = P^U slots per head,
+ * C value channels, Kw / Kr write / read Top-K, E number of leading heads with the CAPE shift.
+ * dtype codes for logits / values / gamma / y: 0 = float32, 1 = float16, 2 = bfloat16.
+ * Slot and mass state, weights and gradients of weights are float32; indices are int32.
+ */
+#ifndef RAMNET_B200_H
+#define RAMNET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { RN_F32 = 0, RN_F16 = 1, RN_BF16 = 2 };
+
+/* Width of the index type used for slot indices (the reference exports the same number as
+ * ramnet_ops._C.INT_BITS, packages/ramnet-ops/csrc/ram_attn_bind.cpp:120-129).  State element
+ * offsets are 64-bit inside the kernels, so B*H*A*C may exceed 2^31. */
+int rn_int_bits(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *rn_last_error(void);
+
+/* Library build tag, e.g. "ramnet_b200 sm_100a". */
+const char *rn_version(void);
+
+/*
+ * Address decode (Product-Softmax over U digit sub-vectors + exact Top-K prefix search +
+ * CAPE cyclic shift), write and read addresses in ONE launch.
+ * Replaces ramnet_ops::topk_addr_forward / topk_addr_single_forward
+ * (packages/ramnet-ops/csrc/ram_attn_ops.cpp:63-97,137-175 and the kernel
+ *  packages/ramnet-ops/csrc/ram_attn_topk_addr.cu:52-117).
+ *
+ *  w_addr, r_addr : logits, logical shape (B,H,U,P,T) addressed through addr_strides[5]
+ *                   (element strides in that order; both tensors share them).  r_addr may be
+ *                   NULL (then Kr must be 0): single-tensor decode.
+ *  pos            : int32 positions, element strides pos_strides[2] over (B,T).
+ *  idx, val       : outputs, logical shape (B,H,Kw+Kr,T) through out_strides[4]; entries
+ *                   [0,Kw) come from w_addr, [Kw,Kw+Kr) from r_addr.  Entry k is the k-th
+ *                   address under (score descending, content index ascending).
+ *  w_neg / r_neg  : store the weight negated (the joined decode of the reference stores reads
+ *                   negated, packages/ramnet-ops/csrc/ram_attn_ops.cpp:152-153).
+ *  encode_batch   : idx = (b*H+h)*A + a when non-zero, h*A + a otherwise.
+ */
+int rn_addr_fwd(const void *w_addr, const void *r_addr, int dtype, const int64_t *addr_strides,
+                const int32_t *pos, const int64_t *pos_strides,
+                int32_t *idx, float *val, const int64_t *out_strides,
+                int64_t B, int64_t H, int64_t U, int64_t P, int64_t T, int64_t E,
+                int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
+                int w_neg, int r_neg, int encode_batch, int device, void *stream);
+
+/*
+ * Gradient of the decoded weights w.r.t. the logits.
+ * Replaces ramnet_ops::topk_addr_backward / topk_addr_single_backward
+ * (packages/ramnet-ops/csrc/ram_attn_ops.cpp:99-135,177-224, kernel
+ *  packages/ramnet-ops/csrc/ram_attn_topk_addr.cu:119-226).
+ *
+ *  idx, val   : forward outputs, (B,H,Kw+Kr,T) through out_strides[4].
+ *  d_val      : upstream gradient w.r.t. the POSITIVE weights, float32, same logical shape,
+ *               strides dval_strides[4].
+ *  d_w, d_r   : outputs in the logits dtype, logical shape (B,H,U,P,T) through dgrad_strides[5];
+ *               d_r may be NULL when Kr == 0.
+ *  w_neg/r_neg: sign convention val was stored with.
+ */
+int rn_addr_bwd(const int32_t *idx, const float *val, const int64_t *out_strides,
+                const float *d_val, const int64_t *dval_strides,
+                const void *w_addr, const void *r_addr, int dtype, const int64_t *addr_strides,
+                const int32_t *pos, const int64_t *pos_strides,
+                void *d_w, void *d_r, const int64_t *dgrad_strides,
+                int64_t B, int64_t H, int64_t U, int64_t P, int64_t T, int64_t E,
+                int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
+                int w_neg, int r_neg, int device, void *stream);
+
+/*
+ * One fused autoregressive decode step: address decode for the write and read logits, gated
+ * update of the Kw selected slots (slot and mass, in place), weighted read of the Kr selected
+ * slots after the update, and optionally the layer epilogue (head-wise RMSNorm and sigmoid
+ * gate).  Replaces ramnet_ops::topk_autoregressive_
+ * (packages/ramnet-ops/csrc/ram_attn_ops.cpp:349-394, kernel
+ *  packages/ramnet-ops/csrc/ram_attn_topk_autoregressive.cu:37-191); the epilogue replaces
+ * packages/ramnet/src/ramnet/layers/ram_attn_block.py:342-348.
+ *
+ *  w_addr, r_addr : (B,H,U,P) contiguous logits;  x : (B,H,C);  gamma : (B,H)   [dtype]
+ *  slot, mass     : float32 state (B,H,A,C) / (B,H,A), contiguous, updated in place
+ *  mask           : (B) bytes, 0 = skip this batch row (state untouched, y = 0); may be NULL
+ *  pos            : (B) int32
+ *  y              : (B,H,C) output in dtype
+ *  norm_weight    : (C) float32 or NULL;  gate_logits : (B,H,C) in dtype or NULL.
+ *                   With either non-NULL, y = RMSNorm(y; norm_eps) * norm_weight * sigmoid(gate).
+ */
+int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
+                   float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
+                   const float *norm_weight, const void *gate_logits, double norm_eps,
+                   int64_t B, int64_t H, int64_t U, int64_t P, int64_t C, int64_t E,
+                   int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
+                   int mass_aware, double eps, int device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RAMNET_B200_H */

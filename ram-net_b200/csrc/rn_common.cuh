@@ -1,0 +1,159 @@
+// Shared host/device helpers for the ramnet_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/ramnet_b200.h"
+
+// ------------------------------------------------------------------------------------------
+// host-side error plumbing: thread-local message + int return code
+// ------------------------------------------------------------------------------------------
+void rn_set_error(const char *fmt, ...);
+void rn_clear_error();
+
+#define RN_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) {                   \
+            rn_set_error(__VA_ARGS__);   \
+            return 1;                    \
+        }                                \
+    } while (0)
+
+#define RN_CUDA(call)                                                                   \
+    do {                                                                                \
+        cudaError_t e_ = (call);                                                        \
+        if (e_ != cudaSuccess) {                                                        \
+            rn_set_error("%s failed: %s", #call, cudaGetErrorString(e_));               \
+            return 2;                                                                   \
+        }                                                                               \
+    } while (0)
+
+// Makes `device` current for the scope of one entry point and restores the previous one.
+struct RnDeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit RnDeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != device && cudaSetDevice(device) != cudaSuccess) ok = false;
+        cur = device;
+    }
+    ~RnDeviceGuard() {
+        if (prev >= 0 && prev != cur) cudaSetDevice(prev);
+    }
+    int cur = -1;
+};
+
+int rn_sm_count(int device);
+
+// ------------------------------------------------------------------------------------------
+// device helpers
+// ------------------------------------------------------------------------------------------
+constexpr unsigned RN_FULL = 0xffffffffu;
+
+template <typename T> __device__ __forceinline__ float rn_to_float(T v);
+template <> __device__ __forceinline__ float rn_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float rn_to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float rn_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T rn_from_float(float v);
+template <> __device__ __forceinline__ float rn_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half rn_from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 rn_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Monotone map float -> uint32 (larger float => larger integer); -0.0 must be canonicalised
+// by the caller (x + 0.0f) so that it ties with +0.0.
+__device__ __forceinline__ uint32_t rn_ord(float f) {
+    uint32_t b = __float_as_uint(f);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+__device__ __forceinline__ float rn_unord(uint32_t o) {
+    return __uint_as_float(o ^ ((o >> 31) ? 0x80000000u : 0xffffffffu));
+}
+// Key whose unsigned order is (score descending-is-larger, index ascending-is-larger):
+// max over keys == best candidate under (score desc, index asc).
+__device__ __forceinline__ uint64_t rn_key(float score, int idx) {
+    return (uint64_t(rn_ord(score + 0.0f)) << 32) | uint32_t(~uint32_t(idx));
+}
+__device__ __forceinline__ float rn_key_score(uint64_t k) { return rn_unord(uint32_t(k >> 32)); }
+__device__ __forceinline__ int rn_key_index(uint64_t k) { return int(~uint32_t(k)); }
+
+__device__ __forceinline__ uint64_t rn_shfl_xor(uint64_t v, int m) {
+    uint32_t lo = __shfl_xor_sync(RN_FULL, uint32_t(v), m);
+    uint32_t hi = __shfl_xor_sync(RN_FULL, uint32_t(v >> 32), m);
+    return (uint64_t(hi) << 32) | lo;
+}
+__device__ __forceinline__ uint64_t rn_shfl(uint64_t v, int src) {
+    uint32_t lo = __shfl_sync(RN_FULL, uint32_t(v), src);
+    uint32_t hi = __shfl_sync(RN_FULL, uint32_t(v >> 32), src);
+    return (uint64_t(hi) << 32) | lo;
+}
+
+__device__ __forceinline__ float rn_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(RN_FULL, v, o));
+    return v;
+}
+__device__ __forceinline__ float rn_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(RN_FULL, v, o);
+    return v;
+}
+
+// Descending bitonic sort of 32*KPL keys held KPL per lane; element e = lane*KPL + r.
+// After the call element 0 is the largest key.
+template <int KPL>
+__device__ __forceinline__ void rn_bitonic_stage(uint64_t (&k)[KPL], int lane, int size, int stride) {
+    // one compare-exchange stage of the classic network over N = 32*KPL elements
+    if (stride >= KPL) {
+        const int lstride = stride / KPL;  // partner lane distance
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            const int e = lane * KPL + r;
+            const uint64_t other = rn_shfl_xor(k[r], lstride);
+            const bool desc = (e & size) == 0;
+            const bool lower = (e & stride) == 0;  // this element is the first of the pair
+            const bool keep_max = (desc == lower);
+            const uint64_t mx = k[r] > other ? k[r] : other;
+            const uint64_t mn = k[r] > other ? other : k[r];
+            k[r] = keep_max ? mx : mn;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            if ((r & stride) == 0) {
+                const int e = lane * KPL + r;
+                const bool desc = (e & size) == 0;
+                uint64_t &a = k[r];
+                uint64_t &b = k[r | stride];
+                const bool sw = desc ? (a < b) : (a > b);
+                if (sw) { uint64_t t = a; a = b; b = t; }
+            }
+        }
+    }
+}
+
+template <int KPL>
+__device__ __forceinline__ void rn_bitonic_sort_desc(uint64_t (&k)[KPL], int lane) {
+    constexpr int N = 32 * KPL;
+#pragma unroll
+    for (int size = 2; size <= N; size <<= 1) {
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            // the final merge (size == N) sorts the whole array descending: (e & N) == 0 always
+            rn_bitonic_stage<KPL>(k, lane, size, stride);
+        }
+    }
+}
+
+// Merge step only: `k` holds a bitonic sequence of N elements; sort it descending.
+template <int KPL>
+__device__ __forceinline__ void rn_bitonic_merge_desc(uint64_t (&k)[KPL], int lane) {
+    constexpr int N = 32 * KPL;
+#pragma unroll
+    for (int stride = N >> 1; stride > 0; stride >>= 1) rn_bitonic_stage<KPL>(k, lane, N, stride);
+}

@@ -1,0 +1,258 @@
+// Fused autoregressive decode step: one CTA per (batch, head).
+//
+//   warp 0 decodes the write address, warp 1 the read address (rn_addr.cuh), warps 2-3 stage x;
+//   the Kw selected slot rows are updated in place (row k -> warp k mod 4, 128-bit accesses when
+//   C is a multiple of 4), then the Kr read rows are gathered after a CTA barrier so a read
+//   of a slot written in this step sees the new value, reduced over K in a fixed order, and the
+//   optional head RMSNorm + sigmoid gate is applied before y is stored in the I/O dtype.
+//
+// State offsets are 64-bit: B*H*A*C may exceed 2^31 elements.
+#include "rn_addr.cuh"
+#include "rn_gsu.cuh"
+
+constexpr int RN_DEC_WARPS = 4;
+constexpr int RN_DEC_CMAX = 1024;
+
+struct RnDecodeParams {
+    const void *w_addr, *r_addr, *x, *gamma;
+    float *slot, *mass;
+    const uint8_t *mask;
+    const int32_t *pos;
+    void *y;
+    const float *norm_weight;
+    const void *gate;
+    float norm_eps;
+    int B, H, U, P, C, E, A;
+    int K[2];
+    float re_norm[2];
+    int mass_aware;
+    float eps;
+};
+
+template <typename T, int KPL, int PPL>
+__global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDecodeParams p) {
+    extern __shared__ float dyn[];  // xs[C] | yred[4][C]
+    __shared__ RnPairTable tabs[2];
+    __shared__ RnWarpScratch scratch[2];
+    __shared__ int row_off[RN_KMAX + 1];
+    __shared__ int sel_slot[2][RN_KMAX];
+    __shared__ float sel_val[2][RN_KMAX];
+    __shared__ float red[RN_DEC_WARPS][2];
+    __shared__ float bcast;
+
+    const int bh = blockIdx.x;
+    const int b = bh / p.H, h = bh % p.H;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int C = p.C;
+    T *y = static_cast<T *>(p.y) + int64_t(bh) * C;
+
+    if (p.mask != nullptr && p.mask[b] == 0) {
+        for (int c = tid; c < C; c += blockDim.x) y[c] = rn_from_float<T>(0.f);
+        return;
+    }
+
+    float *xs = dyn;
+    float *yred = dyn + C;
+
+    rn_build_pairs(&tabs[0], p.K[0], row_off);
+    if (p.K[1] != p.K[0]) rn_build_pairs(&tabs[1], p.K[1], row_off);
+    const RnPairTable *tab_r = (p.K[1] != p.K[0]) ? &tabs[1] : &tabs[0];
+
+    if (warp < 2) {
+        RnDigitLoader<T> load;
+        load.base = static_cast<const T *>(warp == 0 ? p.w_addr : p.r_addr) + int64_t(bh) * p.U * p.P;
+        load.su = p.P;
+        load.sp = 1;
+        const int K = p.K[warp];
+        const RnDecoded<KPL> d =
+            rn_warp_decode<KPL, PPL>(load, p.U, p.P, K, p.re_norm[warp], &scratch[warp], warp == 0 ? &tabs[0] : tab_r, lane);
+        const int shift = (h < p.E) ? rn_pos_mod(p.pos[b], p.A) : 0;
+#pragma unroll
+        for (int r = 0; r < KPL; ++r) {
+            const int e = lane * KPL + r;
+            if (e < K) {
+                sel_slot[warp][e] = rn_cape(d.idx[r], shift, p.A);
+                sel_val[warp][e] = d.val[r];
+            }
+        }
+    } else {
+        const T *x = static_cast<const T *>(p.x) + int64_t(bh) * C;
+        for (int c = tid - 64; c < C; c += 64) xs[c] = rn_to_float<T>(x[c]);
+    }
+    for (int c = tid; c < RN_DEC_WARPS * C; c += blockDim.x) yred[c] = 0.f;
+    __syncthreads();
+
+    const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[bh]);
+    float *slot = p.slot + int64_t(bh) * p.A * C;
+    float *mass = p.mass + int64_t(bh) * p.A;
+    const bool vec4 = (C & 3) == 0;
+
+    // ---- write: gated update of the selected rows ---------------------------------------------
+    for (int k = warp; k < p.K[0]; k += RN_DEC_WARPS) {
+        const float w = sel_val[0][k];
+        if (w == 0.f) continue;
+        const int a = sel_slot[0][k];
+        const RnGate g = rn_gate(w, gamma, mass[a], p.eps);
+        float *row = slot + int64_t(a) * C;
+        if (vec4) {
+            for (int c = lane * 4; c < C; c += 128) {
+                float4 s = *reinterpret_cast<float4 *>(row + c);
+                const float4 xv = *reinterpret_cast<const float4 *>(xs + c);
+                s.x = fmaf(g.gain, xv.x - s.x, s.x);
+                s.y = fmaf(g.gain, xv.y - s.y, s.y);
+                s.z = fmaf(g.gain, xv.z - s.z, s.z);
+                s.w = fmaf(g.gain, xv.w - s.w, s.w);
+                *reinterpret_cast<float4 *>(row + c) = s;
+            }
+        } else {
+            for (int c = lane; c < C; c += 32) row[c] = fmaf(g.gain, xs[c] - row[c], row[c]);
+        }
+        __syncwarp();
+        if (lane == 0) mass[a] = g.mass;
+    }
+    __syncthreads();
+
+    // ---- read: weighted sum of the selected rows (after this step's writes) --------------------
+    float sum_r = 0.f, sum_rm = 0.f;
+    float *acc = yred + warp * C;
+    for (int k = warp; k < p.K[1]; k += RN_DEC_WARPS) {
+        const float r = sel_val[1][k];
+        if (r == 0.f) continue;
+        const int a = sel_slot[1][k];
+        float coef = r;
+        if (p.mass_aware) {
+            coef = r * mass[a];
+            sum_r += r;
+            sum_rm += coef;
+        }
+        const float *row = slot + int64_t(a) * C;
+        if (vec4) {
+            for (int c = lane * 4; c < C; c += 128) {
+                const float4 s = *reinterpret_cast<const float4 *>(row + c);
+                float4 o = *reinterpret_cast<float4 *>(acc + c);
+                o.x = fmaf(coef, s.x, o.x);
+                o.y = fmaf(coef, s.y, o.y);
+                o.z = fmaf(coef, s.z, o.z);
+                o.w = fmaf(coef, s.w, o.w);
+                *reinterpret_cast<float4 *>(acc + c) = o;
+            }
+        } else {
+            for (int c = lane; c < C; c += 32) acc[c] = fmaf(coef, row[c], acc[c]);
+        }
+    }
+    if (lane == 0) {
+        red[warp][0] = sum_r;
+        red[warp][1] = sum_rm;
+    }
+    __syncthreads();
+
+    float scale = 1.f;
+    if (p.mass_aware) {
+        float sr = 0.f, srm = 0.f;
+        for (int w = 0; w < RN_DEC_WARPS; ++w) {
+            sr += red[w][0];
+            srm += red[w][1];
+        }
+        scale = sr / (srm + p.eps);
+    }
+    const bool epilogue = p.norm_weight != nullptr || p.gate != nullptr;
+    float sq = 0.f;
+    for (int c = tid; c < C; c += blockDim.x) {
+        float v = 0.f;
+        for (int w = 0; w < RN_DEC_WARPS; ++w) v += yred[w * C + c];
+        v *= scale;
+        if (epilogue) {
+            yred[c] = v;  // column c is owned by this thread in every pass
+            sq += v * v;
+        } else {
+            y[c] = rn_from_float<T>(v);
+        }
+    }
+    if (!epilogue) return;
+
+    float inv_rms = 1.f;
+    if (p.norm_weight != nullptr) {
+        sq = rn_warp_sum(sq);
+        __syncthreads();  // red[] is reused
+        if (lane == 0) red[warp][0] = sq;
+        __syncthreads();
+        if (tid == 0) {
+            float s = 0.f;
+            for (int w = 0; w < RN_DEC_WARPS; ++w) s += red[w][0];
+            bcast = rsqrtf(s / float(C) + p.norm_eps);
+        }
+        __syncthreads();
+        inv_rms = bcast;
+    }
+    const T *gate = p.gate ? static_cast<const T *>(p.gate) + int64_t(bh) * C : nullptr;
+    for (int c = tid; c < C; c += blockDim.x) {
+        float v = yred[c];
+        if (p.norm_weight != nullptr) v = v * inv_rms * p.norm_weight[c];
+        if (gate != nullptr) v = v / (1.f + expf(-rn_to_float<T>(gate[c])));
+        y[c] = rn_from_float<T>(v);
+    }
+}
+
+static int rn_per_lane_dec(int64_t n) { return n <= 32 ? 1 : (n <= 64 ? 2 : 4); }
+
+template <typename T>
+static int rn_launch_decode(const RnDecodeParams &p, int kpl, int ppl, int grid, size_t smem, cudaStream_t stream) {
+#define RN_CASE(KP, PP)                                                                       \
+    if (kpl == KP && ppl == PP) {                                                             \
+        rn_decode_kernel<T, KP, PP><<<grid, RN_DEC_WARPS * 32, smem, stream>>>(p);            \
+        return 0;                                                                             \
+    }
+    RN_CASE(1, 1) RN_CASE(1, 2) RN_CASE(1, 4) RN_CASE(2, 1) RN_CASE(2, 2) RN_CASE(2, 4) RN_CASE(4, 1) RN_CASE(4, 2)
+    RN_CASE(4, 4)
+#undef RN_CASE
+    rn_set_error("no decode kernel for K-per-lane=%d, P-per-lane=%d", kpl, ppl);
+    return 1;
+}
+
+extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
+                              float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
+                              const float *norm_weight, const void *gate_logits, double norm_eps, int64_t B, int64_t H,
+                              int64_t U, int64_t P, int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm,
+                              double r_re_norm, int mass_aware, double eps, int device, void *stream) {
+    rn_clear_error();
+    RN_REQUIRE(w_addr && r_addr && x && gamma && slot && mass && pos && y, "null pointer argument");
+    RN_REQUIRE(B > 0 && H > 0 && U > 0 && P > 0 && C > 0, "decode dims must be positive");
+    RN_REQUIRE(U <= RN_UMAX, "Expect U <= %d but got %lld", RN_UMAX, (long long)U);
+    RN_REQUIRE(P <= RN_PMAX, "Expect P <= %d but got %lld", RN_PMAX, (long long)P);
+    RN_REQUIRE(C <= RN_DEC_CMAX, "Expect C <= %d but got %lld", RN_DEC_CMAX, (long long)C);
+    int64_t A = 1;
+    for (int64_t u = 0; u < U; ++u) {
+        A *= P;
+        RN_REQUIRE(A < (int64_t(1) << 30), "Address space overflow: P^U must stay below 2^30");
+    }
+    RN_REQUIRE(Kw > 0 && Kw <= RN_KMAX && Kw <= A, "Expect 0 < w_top_k <= min(%d, A) but got %lld", RN_KMAX, (long long)Kw);
+    RN_REQUIRE(Kr > 0 && Kr <= RN_KMAX && Kr <= A, "Expect 0 < r_top_k <= min(%d, A) but got %lld", RN_KMAX, (long long)Kr);
+    RN_REQUIRE(E >= 0 && E <= H, "Expect embed_num in [0, H]");
+    RN_REQUIRE(w_re_norm >= 0.0 && w_re_norm <= 1.0, "w_re_norm must be in [0, 1].");
+    RN_REQUIRE(r_re_norm >= 0.0 && r_re_norm <= 1.0, "r_re_norm must be in [0, 1].");
+    RN_REQUIRE(dtype == RN_F32 || dtype == RN_F16 || dtype == RN_BF16, "unsupported dtype code %d", dtype);
+    RN_REQUIRE(B * H < (int64_t(1) << 31), "B*H too large");
+    RN_REQUIRE((reinterpret_cast<uintptr_t>(slot) & 15) == 0, "slot must be 16-byte aligned");
+    RnDeviceGuard guard(device);
+    RN_REQUIRE(guard.ok, "cannot make device %d current", device);
+
+    RnDecodeParams p{};
+    p.w_addr = w_addr; p.r_addr = r_addr; p.x = x; p.gamma = gamma;
+    p.slot = slot; p.mass = mass; p.mask = mask; p.pos = pos; p.y = y;
+    p.norm_weight = norm_weight; p.gate = gate_logits; p.norm_eps = float(norm_eps);
+    p.B = int(B); p.H = int(H); p.U = int(U); p.P = int(P); p.C = int(C); p.E = int(E); p.A = int(A);
+    p.K[0] = int(Kw); p.K[1] = int(Kr);
+    p.re_norm[0] = float(w_re_norm); p.re_norm[1] = float(r_re_norm);
+    p.mass_aware = mass_aware; p.eps = float(eps);
+
+    const int kpl = rn_per_lane_dec(Kw > Kr ? Kw : Kr), ppl = rn_per_lane_dec(P);
+    const size_t smem = size_t(C) * (1 + RN_DEC_WARPS) * sizeof(float);
+    const int grid = int(B * H);
+    int rc;
+    if (dtype == RN_F32) rc = rn_launch_decode<float>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
+    else if (dtype == RN_F16) rc = rn_launch_decode<__half>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
+    else rc = rn_launch_decode<__nv_bfloat16>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
+    if (rc) return rc;
+    RN_CUDA(cudaGetLastError());
+    return 0;
+}

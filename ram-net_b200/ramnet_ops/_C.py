@@ -1,0 +1,72 @@
+"""Native module of ramnet_ops: loads libramnet_b200.so (C ABI, see include/ramnet_b200.h) and
+defines the ``torch.ops.ramnet_ops.*`` operator schemas with their CUDA implementations.
+
+Plays the role of the reference's compiled ``ramnet_ops._C``
+(packages/ramnet-ops/csrc/ram_attn_bind.cpp:27-129): importing it registers the operators and
+exposes ``INT_BITS``.  There is no CPU implementation behind these operators and no fallback:
+if the shared library is missing, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "libramnet_b200.so"
+if not _LIB_PATH.exists():
+    raise ImportError(
+        f"{_LIB_PATH} is missing: build it with `python ram-net_b200/build.py` (needs nvcc); "
+        "ramnet_ops has no CPU fallback for its CUDA operators.")
+
+lib = ctypes.CDLL(str(_LIB_PATH))
+
+_i64, _i32, _f64, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_double, ctypes.c_void_p
+_i64p = ctypes.POINTER(ctypes.c_int64)
+
+lib.rn_int_bits.restype = ctypes.c_int
+lib.rn_last_error.restype = ctypes.c_char_p
+lib.rn_version.restype = ctypes.c_char_p
+
+lib.rn_addr_fwd.restype = ctypes.c_int
+lib.rn_addr_fwd.argtypes = [_ptr, _ptr, _i32, _i64p, _ptr, _i64p, _ptr, _ptr, _i64p,
+                            _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f64, _f64, _i32, _i32, _i32, _i32, _ptr]
+lib.rn_addr_bwd.restype = ctypes.c_int
+lib.rn_addr_bwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _ptr, _i32, _i64p, _ptr, _i64p, _ptr, _ptr, _i64p,
+                            _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f64, _f64, _i32, _i32, _i32, _ptr]
+lib.rn_decode_step.restype = ctypes.c_int
+lib.rn_decode_step.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _f64,
+                               _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f64, _f64, _i32, _f64, _i32, _ptr]
+
+INT_BITS: int = int(lib.rn_int_bits())
+
+DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def check(rc: int) -> None:
+    """Turn a non-zero C-ABI return code into RuntimeError (the reference raises the same type
+    from its TORCH_CHECKs, packages/ramnet-ops/csrc/torch_compat.h:19-22)."""
+    if rc != 0:
+        raise RuntimeError(lib.rn_last_error().decode())
+
+
+def strides(t: torch.Tensor):
+    return (ctypes.c_int64 * t.dim())(*t.stride())
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_of(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"ramnet_ops CUDA kernels support float32/float16/bfloat16, got {t.dtype}") from None
+
+
+from . import _ops  # noqa: E402,F401  (defines torch.ops.ramnet_ops.* on import)

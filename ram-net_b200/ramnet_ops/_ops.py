@@ -1,0 +1,197 @@
+"""Operator schemas of the ``ramnet_ops`` namespace and their CUDA implementations.
+
+The eight schemas are those of the reference dispatcher library
+(packages/ramnet-ops/csrc/ram_attn_bind.cpp:27-101); the ``gsu_*`` and ``decode_fused_``
+operators are additions used by this package's own call path.  Every implementation
+allocates its outputs with PyTorch (caching allocator, CUDA-graph friendly) and hands raw
+pointers, sizes and strides to the C ABI; nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _C
+from ._C import check, dtype_code, lib, ptr, stream_of, strides
+
+_lib = torch.library.Library("ramnet_ops", "DEF")
+
+_lib.define(
+    "topk_addr_single_forward(Tensor addr, int embed_num, int A, Tensor position_ids, int top_k, float top_k_re_norm, "
+    "bool addr_val_neg=False, bool encode_batch_idx=True) -> (Tensor, Tensor)")
+_lib.define(
+    "topk_addr_single_backward(Tensor idx, Tensor val, Tensor addr, Tensor D_val, int embed_num, Tensor position_ids, "
+    "int top_k, float top_k_re_norm, bool addr_val_neg, int[] shape, ScalarType dtype) -> Tensor")
+_lib.define(
+    "topk_addr_forward(Tensor w_addr, Tensor r_addr, int embed_num, int A, Tensor position_ids, int w_top_k, int r_top_k, "
+    "float w_re_norm, float r_re_norm, bool encode_batch_idx=True) -> (Tensor, Tensor)")
+_lib.define(
+    "topk_addr_backward(Tensor idx, Tensor val, Tensor w_addr, Tensor r_addr, Tensor D_val, int embed_num, "
+    "Tensor position_ids, int w_top_k, int r_top_k, float w_re_norm, float r_re_norm, int[] shape, ScalarType dtype) "
+    "-> (Tensor, Tensor)")
+_lib.define(
+    "topk_autoregressive_(Tensor w_addr, Tensor r_addr, Tensor x, Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, "
+    "Tensor mask, int embed_num, Tensor position_ids, int w_top_k, int r_top_k, float w_re_norm, float r_re_norm, "
+    "bool mass_aware, float eps) -> Tensor")
+_lib.define(
+    "decode_fused_(Tensor w_addr, Tensor r_addr, Tensor x, Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, "
+    "Tensor mask, int embed_num, Tensor position_ids, int w_top_k, int r_top_k, float w_re_norm, float r_re_norm, "
+    "bool mass_aware, float eps, Tensor? norm_weight, Tensor? gate_logits, float norm_eps) -> Tensor")
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("ramnet_ops CUDA operators need CUDA tensors")
+
+
+def _int32(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.int32 else t.to(torch.int32)
+
+
+def _slots(addr: torch.Tensor, A: int) -> None:
+    U, P = addr.shape[2], addr.shape[3]
+    if A != P ** U:
+        raise RuntimeError(f"A={A} does not equal P**U={P ** U}")
+
+
+def _new_token_major(like: torch.Tensor, B: int, H: int, K: int, T: int, dtype: torch.dtype) -> torch.Tensor:
+    """(B,H,K,T)-shaped tensor stored token-major (B,T,H,K): one token-head's K entries are contiguous."""
+    return torch.empty((B, T, H, K), dtype=dtype, device=like.device).permute(0, 2, 3, 1)
+
+
+def _new_logit_grad(like: torch.Tensor, B: int, H: int, U: int, P: int, T: int, dtype: torch.dtype) -> torch.Tensor:
+    return torch.empty((B, T, H, U, P), dtype=dtype, device=like.device).permute(0, 2, 3, 4, 1)
+
+
+# ----------------------------------------------------------------------------------------------
+# address decode
+# ----------------------------------------------------------------------------------------------
+def addr_forward_impl(w_addr, r_addr, embed_num, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm,
+                      w_neg, r_neg, encode_batch_idx):
+    _require_cuda(w_addr, r_addr, position_ids)
+    B, H, U, P, T = w_addr.shape
+    if r_addr is not None and r_addr.stride() != w_addr.stride():
+        w_addr, r_addr = w_addr.contiguous(), r_addr.contiguous()
+    pos = _int32(position_ids)
+    K = w_top_k + r_top_k
+    idx = _new_token_major(w_addr, B, H, K, T, torch.int32)
+    val = _new_token_major(w_addr, B, H, K, T, torch.float32)
+    if idx.numel() == 0:
+        return idx, val
+    check(lib.rn_addr_fwd(ptr(w_addr), ptr(r_addr), dtype_code(w_addr), strides(w_addr), ptr(pos), strides(pos),
+                          ptr(idx), ptr(val), strides(idx), B, H, U, P, T, embed_num, w_top_k, r_top_k,
+                          float(w_re_norm), float(r_re_norm), int(w_neg), int(r_neg), int(encode_batch_idx),
+                          w_addr.device.index, stream_of(w_addr)))
+    return idx, val
+
+
+def addr_backward_impl(idx, val, w_addr, r_addr, d_val, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
+                       r_re_norm, w_neg, r_neg, dtype):
+    _require_cuda(idx, val, w_addr, r_addr, d_val, position_ids)
+    B, H, U, P, T = w_addr.shape
+    if r_addr is not None and r_addr.stride() != w_addr.stride():
+        w_addr, r_addr = w_addr.contiguous(), r_addr.contiguous()
+    if w_addr.dtype != dtype:
+        w_addr = w_addr.to(dtype)
+        r_addr = None if r_addr is None else r_addr.to(dtype)
+    if val.stride() != idx.stride():
+        val = val.contiguous()
+        idx = idx.contiguous()
+    pos = _int32(position_ids)
+    d_val = d_val.to(torch.float32)
+    d_w = _new_logit_grad(w_addr, B, H, U, P, T, dtype)
+    d_r = _new_logit_grad(w_addr, B, H, U, P, T, dtype) if r_addr is not None else None
+    if d_w.numel() == 0:
+        return d_w, d_r
+    check(lib.rn_addr_bwd(ptr(idx), ptr(val), strides(idx), ptr(d_val), strides(d_val), ptr(w_addr), ptr(r_addr),
+                          dtype_code(w_addr), strides(w_addr), ptr(pos), strides(pos), ptr(d_w), ptr(d_r), strides(d_w),
+                          B, H, U, P, T, embed_num, w_top_k, r_top_k, float(w_re_norm), float(r_re_norm),
+                          int(w_neg), int(r_neg), w_addr.device.index, stream_of(w_addr)))
+    return d_w, d_r
+
+
+@torch.library.impl(_lib, "topk_addr_single_forward", "CUDA")
+def _topk_addr_single_forward(addr, embed_num, A, position_ids, top_k, top_k_re_norm, addr_val_neg=False,
+                              encode_batch_idx=True):
+    _slots(addr, A)
+    return addr_forward_impl(addr, None, embed_num, position_ids, top_k, 0, top_k_re_norm, 0.0, addr_val_neg, False,
+                             encode_batch_idx)
+
+
+@torch.library.impl(_lib, "topk_addr_single_backward", "CUDA")
+def _topk_addr_single_backward(idx, val, addr, D_val, embed_num, position_ids, top_k, top_k_re_norm, addr_val_neg,
+                               shape, dtype):
+    if len(shape) != 6:
+        raise RuntimeError("Expected address dimensions (B, H, U, P, A, T).")
+    # D_val is the gradient of the stored (signed) value; the kernel wants it w.r.t. the positive weight
+    d_pos = -D_val if addr_val_neg else D_val
+    d_w, _ = addr_backward_impl(idx, val, addr, None, d_pos, embed_num, position_ids, top_k, 0, top_k_re_norm, 0.0,
+                                addr_val_neg, False, dtype)
+    return d_w
+
+
+@torch.library.impl(_lib, "topk_addr_forward", "CUDA")
+def _topk_addr_forward(w_addr, r_addr, embed_num, A, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm,
+                       encode_batch_idx=True):
+    _slots(w_addr, A)
+    # joined decode: writes keep a positive sign, reads are stored negated
+    return addr_forward_impl(w_addr, r_addr, embed_num, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm, False,
+                             True, encode_batch_idx)
+
+
+@torch.library.impl(_lib, "topk_addr_backward", "CUDA")
+def _topk_addr_backward(idx, val, w_addr, r_addr, D_val, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
+                        r_re_norm, shape, dtype):
+    if len(shape) != 6:
+        raise RuntimeError("Expected address dimensions (B, H, U, P, A, T).")
+    return addr_backward_impl(idx, val, w_addr, r_addr, D_val, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
+                              r_re_norm, False, True, dtype)
+
+
+# ----------------------------------------------------------------------------------------------
+# fused decode step
+# ----------------------------------------------------------------------------------------------
+def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
+                r_re_norm, mass_aware, eps, norm_weight=None, gate_logits=None, norm_eps=0.0):
+    _require_cuda(w_addr, r_addr, x, gamma, slot, mass, position_ids)
+    B, H, U, P = w_addr.shape
+    C = x.shape[-1]
+    if slot.dtype != torch.float32 or mass.dtype != torch.float32:
+        raise RuntimeError(f"slot/mass state must be float32, got {slot.dtype}/{mass.dtype}")
+    if not (slot.is_contiguous() and mass.is_contiguous()):
+        raise RuntimeError("Tensor slot/mass must be contiguous")
+    if tuple(slot.shape) != (B, H, P ** U, C) or tuple(mass.shape) != (B, H, P ** U):
+        raise RuntimeError(f"state shape mismatch: slot {tuple(slot.shape)}, mass {tuple(mass.shape)}")
+    w_addr, r_addr, x, gamma = (t.contiguous() for t in (w_addr, r_addr, x, gamma))
+    if not (r_addr.dtype == x.dtype == gamma.dtype == w_addr.dtype):
+        raise RuntimeError("w_addr, r_addr, x and gamma must share one dtype")
+    pos = _int32(position_ids).contiguous()
+    mask_u8 = None
+    if mask is not None and mask.numel() > 0:
+        mask_u8 = mask.to(torch.bool).contiguous().view(torch.uint8)
+    if norm_weight is not None:
+        norm_weight = norm_weight.to(torch.float32).contiguous()
+    if gate_logits is not None:
+        gate_logits = gate_logits.to(x.dtype).contiguous()
+    y = torch.empty_like(x)
+    if y.numel() == 0:
+        return y
+    check(lib.rn_decode_step(ptr(w_addr), ptr(r_addr), ptr(x), ptr(gamma), dtype_code(x), ptr(slot), ptr(mass),
+                             ptr(mask_u8), ptr(pos), ptr(y), ptr(norm_weight), ptr(gate_logits), float(norm_eps),
+                             B, H, U, P, C, embed_num, w_top_k, r_top_k, float(w_re_norm), float(r_re_norm),
+                             int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    return y
+
+
+@torch.library.impl(_lib, "topk_autoregressive_", "CUDA")
+def _topk_autoregressive_(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k,
+                          w_re_norm, r_re_norm, mass_aware, eps):
+    return decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k,
+                       w_re_norm, r_re_norm, mass_aware, eps)
+
+
+@torch.library.impl(_lib, "decode_fused_", "CUDA")
+def _decode_fused_(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
+                   r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps):
+    return decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k,
+                       w_re_norm, r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps)
