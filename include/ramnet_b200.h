@@ -106,6 +106,33 @@ int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const 
                    int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
                    int mass_aware, double eps, int device, void *stream);
 
+/*
+ * Prefill (T > 1) gated sparse update + read over decoded addresses.
+ * Replaces gather_segment + ramnet_ops::topk_segment_forward / topk_segment_forward_
+ * (packages/ramnet-ops/src/ramnet_ops/impl/cuda_impl.py:72-141,
+ *  packages/ramnet-ops/csrc/ram_attn_ops.cpp:226-265,312-347, kernel
+ *  packages/ramnet-ops/csrc/ram_attn_segment_parallel.cu:241-416).
+ *
+ *  idx, val     : decoded addresses, logical (B,H,Kw+Kr,T) through idx_strides[4] (shared by
+ *                 both); entries [0,Kw) are writes, [Kw,Kw+Kr) reads; |val| is the weight,
+ *                 val == 0 marks a no-op; idx may carry the (b*H+h)*A offset (idx mod A is used).
+ *  x            : (B,H,T,C) values through x_strides[4] (channel stride 1);
+ *  gamma        : (B,H,T) through gamma_strides[3];  mask: (B,T) bytes through mask_strides[2]
+ *                 or NULL; a masked token neither writes nor reads and its y is zero.
+ *  slot_in/mass_in, slot_out/mass_out : float32 contiguous (B,H,A,C)/(B,H,A); out may alias in.
+ *  y            : (B,H,T,C) through y_strides[4] (channel stride 1), written in dtype.
+ *  workspace    : caller-owned scratch of at least rn_gsu_workspace_bytes(...) bytes, 256-byte
+ *                 aligned; holds the per-chunk event schedule between the two kernels.
+ */
+int64_t rn_gsu_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
+                               int device);
+int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *idx_strides, const void *x,
+               const int64_t *x_strides, const void *gamma, const int64_t *gamma_strides, int dtype,
+               const uint8_t *mask, const int64_t *mask_strides, const float *slot_in, const float *mass_in,
+               float *slot_out, float *mass_out, void *y, const int64_t *y_strides, void *workspace,
+               int64_t workspace_bytes, int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw,
+               int64_t Kr, int mass_aware, double eps, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -208,7 +208,9 @@ __device__ __forceinline__ RnDecoded<KPL> rn_warp_decode(const Loader &load, int
     for (int r = 0; r < KPL; ++r) {
         const int e = lane * KPL + r;
         out.val[r] = (e < K && !inactive) ? expf(logq[r]) : 0.f;
-        if (inactive) out.idx[r] = e;  // every score ties: canonical order is 0, 1, 2, ...
+        // inactive token: every score ties, canonical order is 0, 1, 2, ...; an entry with score
+        // -inf is a zero-weight no-op and reports its rank as well
+        if (inactive || logq[r] == -INFINITY) out.idx[r] = e;
     }
     __syncwarp();
     return out;

@@ -38,6 +38,12 @@ lib.rn_decode_step.restype = ctypes.c_int
 lib.rn_decode_step.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _f64,
                                _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f64, _f64, _i32, _f64, _i32, _ptr]
 
+lib.rn_gsu_workspace_bytes.restype = ctypes.c_int64
+lib.rn_gsu_workspace_bytes.argtypes = [_i64] * 7 + [_i32]
+lib.rn_gsu_fwd.restype = ctypes.c_int
+lib.rn_gsu_fwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _i64p, _i32, _ptr, _i64p, _ptr, _ptr, _ptr, _ptr, _ptr,
+                           _i64p, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _f64, _i32, _ptr]
+
 INT_BITS: int = int(lib.rn_int_bits())
 
 DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}

@@ -36,6 +36,12 @@ _lib.define(
     "decode_fused_(Tensor w_addr, Tensor r_addr, Tensor x, Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, "
     "Tensor mask, int embed_num, Tensor position_ids, int w_top_k, int r_top_k, float w_re_norm, float r_re_norm, "
     "bool mass_aware, float eps, Tensor? norm_weight, Tensor? gate_logits, float norm_eps) -> Tensor")
+_lib.define(
+    "gsu_forward(Tensor addr_idx, Tensor addr_val, Tensor x, Tensor gamma, Tensor init_slot, Tensor init_mass, "
+    "Tensor? mask, int w_top_k, int r_top_k, bool mass_aware, float eps) -> (Tensor, Tensor, Tensor)")
+_lib.define(
+    "gsu_forward_(Tensor addr_idx, Tensor addr_val, Tensor x, Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, "
+    "Tensor? mask, int w_top_k, int r_top_k, bool mass_aware, float eps) -> Tensor")
 
 
 def _require_cuda(*tensors: torch.Tensor) -> None:
@@ -195,3 +201,66 @@ def _decode_fused_(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, positi
                    r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps):
     return decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k,
                        w_re_norm, r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps)
+
+
+# ----------------------------------------------------------------------------------------------
+# prefill: gated sparse update + read over decoded addresses
+# ----------------------------------------------------------------------------------------------
+def gsu_forward_impl(addr_idx, addr_val, x, gamma, slot_in, mass_in, slot_out, mass_out, mask, w_top_k, r_top_k,
+                     mass_aware, eps, y_dtype=None):
+    """Launch the schedule + apply kernels.  ``slot_out``/``mass_out`` may alias the inputs."""
+    _require_cuda(addr_idx, addr_val, x, gamma, slot_in, mass_in)
+    B, H, T, C = x.shape
+    A = slot_in.shape[2]
+    if tuple(addr_idx.shape) != (B, H, w_top_k + r_top_k, T) or addr_val.shape != addr_idx.shape:
+        raise RuntimeError(f"Tensor addr_idx/addr_val shape mismatch: expect {(B, H, w_top_k + r_top_k, T)}, "
+                           f"but got {tuple(addr_idx.shape)} / {tuple(addr_val.shape)}")
+    for name, s in (("slot", slot_in), ("mass", mass_in), ("slot", slot_out), ("mass", mass_out)):
+        if s.dtype != torch.float32 or not s.is_contiguous():
+            raise RuntimeError(f"Tensor {name} must be contiguous float32")
+    if tuple(slot_in.shape) != (B, H, A, C) or tuple(mass_in.shape) != (B, H, A):
+        raise RuntimeError(f"state shape mismatch: slot {tuple(slot_in.shape)}, mass {tuple(mass_in.shape)}")
+    if addr_val.dtype != torch.float32 or addr_idx.dtype != torch.int32:
+        raise RuntimeError("addr_idx must be int32 and addr_val float32")
+    if addr_val.stride() != addr_idx.stride():
+        addr_idx, addr_val = addr_idx.contiguous(), addr_val.contiguous()
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if gamma.dtype != x.dtype:
+        raise RuntimeError(f"Tensor gamma type mismatch: expect {x.dtype}, but got {gamma.dtype}")
+    y_dtype = x.dtype if y_dtype is None else y_dtype
+    if y_dtype != x.dtype:
+        raise RuntimeError("y is produced in the dtype of x")
+    y = torch.empty((B, T, H, C), dtype=x.dtype, device=x.device).permute(0, 2, 1, 3)
+    if y.numel() == 0:
+        if slot_out.data_ptr() != slot_in.data_ptr():
+            slot_out.copy_(slot_in)
+            mass_out.copy_(mass_in)
+        return y
+    mask_u8 = None
+    if mask is not None:
+        mask_u8 = mask.to(torch.bool).view(torch.uint8)
+    nbytes = lib.rn_gsu_workspace_bytes(B, H, T, A, C, w_top_k, r_top_k, x.device.index)
+    if nbytes < 0:
+        check(1)
+    ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=x.device)
+    check(lib.rn_gsu_fwd(ptr(addr_idx), ptr(addr_val), strides(addr_idx), ptr(x), strides(x), ptr(gamma), strides(gamma),
+                         dtype_code(x), ptr(mask_u8), None if mask_u8 is None else strides(mask_u8), ptr(slot_in),
+                         ptr(mass_in), ptr(slot_out), ptr(mass_out), ptr(y), strides(y), ptr(ws), int(nbytes), B, H, T,
+                         A, C, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    return y
+
+
+@torch.library.impl(_lib, "gsu_forward", "CUDA")
+def _gsu_forward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, w_top_k, r_top_k, mass_aware, eps):
+    slot_in = init_slot.to(torch.float32).contiguous()
+    mass_in = init_mass.to(torch.float32).contiguous()
+    slot_out, mass_out = torch.empty_like(slot_in), torch.empty_like(mass_in)
+    y = gsu_forward_impl(addr_idx, addr_val, x, gamma, slot_in, mass_in, slot_out, mass_out, mask, w_top_k, r_top_k,
+                         mass_aware, eps)
+    return y, slot_out, mass_out
+
+
+@torch.library.impl(_lib, "gsu_forward_", "CUDA")
+def _gsu_forward_(addr_idx, addr_val, x, gamma, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps):
+    return gsu_forward_impl(addr_idx, addr_val, x, gamma, slot, mass, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps)

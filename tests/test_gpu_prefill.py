@@ -1,0 +1,152 @@
+"""GPU parity of the prefill path (address decode -> schedule -> apply) against the CPU oracle and
+the reference golden vectors, through torch.ops.ramnet_ops -> C ABI."""
+import pytest
+import torch
+
+from oracle import ramnet_oracle as orc
+from tests.gpu_common import ops, randn
+from tests.helpers import BF16_TOL, FP16_TOL, FP32_TOL, assert_close_stats, load, t
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu(w, r, x, g, slot, mass, mask, E, pos, K, renorm, mass_aware, eps, inplace=False):
+    """w/r (B,H,U,P,T), x (B,H,T,C), g (B,H,T) on CPU -> GPU forward; returns CPU tensors."""
+    ops()
+    P, U = w.shape[3], w.shape[2]
+    dev = "cuda"
+    idx, val = torch.ops.ramnet_ops.topk_addr_forward(w.to(dev), r.to(dev), E, P ** U, pos.to(dev).int(), K[0], K[1],
+                                                      renorm[0], renorm[1])
+    m = None if mask is None else mask.to(dev)
+    if inplace:
+        s, ms = slot.clone().to(dev), mass.clone().to(dev)
+        y = torch.ops.ramnet_ops.gsu_forward_(idx, val, x.to(dev), g.to(dev), s, ms, m, K[0], K[1], mass_aware, eps)
+    else:
+        y, s, ms = torch.ops.ramnet_ops.gsu_forward(idx, val, x.to(dev), g.to(dev), slot.to(dev), mass.to(dev), m,
+                                                    K[0], K[1], mass_aware, eps)
+    torch.cuda.synchronize()
+    return y.cpu(), s.cpu(), ms.cpu()
+
+
+def make_case(B, H, U, P, T, C, dtype, seed, zero_state=False, masked=False):
+    A = P ** U
+    w = randn((B, T, H, U, P), seed, dtype).permute(0, 2, 3, 4, 1)
+    r = randn((B, T, H, U, P), seed + 1, dtype).permute(0, 2, 3, 4, 1)
+    x = randn((B, T, H, C), seed + 2, dtype).permute(0, 2, 1, 3)
+    g = (0.5 * randn((B, T, H), seed + 3)).to(dtype).permute(0, 2, 1)
+    if zero_state:
+        slot, mass = torch.zeros(B, H, A, C), torch.full((B, H, A), 1.0 / A)
+    else:
+        slot = randn((B, H, A, C), seed + 4)
+        mass = torch.rand(B, H, A, generator=torch.Generator().manual_seed(seed + 5)) + 0.1
+    if masked:
+        mask = torch.ones(B, T, dtype=torch.bool)
+        mask[:, : max(1, T // 8)] = False
+        mask[0, T // 2: T // 2 + 3] = False
+        mask[:, -2:] = False
+        pos = ((mask.long().cumsum(-1) - 1) * 3 + 11).masked_fill(~mask, 0)
+    else:
+        mask, pos = None, torch.arange(T).view(1, T).expand(B, T).contiguous()
+    return w, r, x, g, slot, mass, mask, pos
+
+
+def check(name, got, ref, mask, dtype):
+    y, s, m = got
+    ry, rs, rm = ref
+    tol = {torch.float32: FP32_TOL, torch.bfloat16: BF16_TOL, torch.float16: FP16_TOL}[dtype]
+    if mask is not None:
+        assert float(y.float().permute(0, 2, 1, 3)[~mask].abs().max()) == 0.0
+        y, ry = y.permute(0, 2, 1, 3)[mask], ry.permute(0, 2, 1, 3)[mask]
+    assert_close_stats(name + ".y", y.float(), ry.float(), **tol)
+    assert_close_stats(name + ".slot", s, rs, **FP32_TOL)
+    assert_close_stats(name + ".mass", m, rm, **FP32_TOL)
+
+
+CASES = [
+    # B, H, U, P, T, C, K, dtype, masked, mass_aware
+    (1, 4, 2, 16, 130, 64, (4, 4), torch.float32, False, False),
+    (2, 3, 2, 6, 40, 10, (3, 5), torch.float32, True, False),
+    (2, 3, 2, 6, 40, 10, (3, 5), torch.float32, True, True),
+    (1, 2, 3, 4, 33, 7, (8, 8), torch.float32, False, False),
+    (2, 2, 2, 64, 96, 128, (16, 16), torch.bfloat16, False, False),
+    (1, 2, 2, 2, 150, 5, (2, 3), torch.float32, False, True),      # 4 slots: long same-slot chains
+    (1, 2, 4, 3, 65, 29, (4, 12), torch.float16, True, False),
+    (1, 2, 5, 4, 70, 32, (128, 128), torch.float32, False, False),  # chunk length 16
+    (1, 2, 3, 32, 40, 16, (8, 8), torch.bfloat16, False, True),     # A = 32768: slot state stays in global memory
+    (1, 1, 2, 128, 20, 8, (5, 7), torch.float32, False, False),     # A = 16384
+    (1, 2, 4, 7, 64, 65, (8, 8), torch.float32, True, True),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_prefill_matches_oracle(case):
+    B, H, U, P, T, C, K, dtype, masked, ma = case
+    w, r, x, g, slot, mass, mask, pos = make_case(B, H, U, P, T, C, dtype, 3, masked=masked)
+    renorm, eps, E = (0.25, 0.75), 1e-6, H // 2
+    got = run_gpu(w, r, x, g, slot, mass, mask, E, pos, K, renorm, ma, eps)
+    ref = orc.ram_attn(w.float(), r.float(), x.float(), g.float(), slot, mass, mask, E, pos, K, renorm, ma, eps)
+    check("prefill", got, ref, mask, dtype)
+    assert got[0].dtype == dtype
+
+
+@pytest.mark.parametrize("name", ["ram_config1.npz", "ram_grads_masked.npz", "ram_grads_massaware.npz",
+                                  "ram_grads_plain.npz", "ram_bf16_u2p16.npz"])
+def test_prefill_matches_reference_golden(name):
+    z = load(name)
+    B, H, U, P, T, Kw, Kr, C, E, ma = (int(v) for v in z["meta"])
+    dtype = torch.bfloat16 if "bfloat16" in str(z["in_dtype"]) else torch.float32
+    mask = t(z["mask"]) if z["mask"].size else None
+    w = t(z["w_addr"]).to(dtype).permute(0, 2, 3, 4, 1)
+    r = t(z["r_addr"]).to(dtype).permute(0, 2, 3, 4, 1)
+    x = t(z["values"]).to(dtype).permute(0, 2, 1, 3)
+    g = t(z["gamma"]).to(dtype).permute(0, 2, 1)
+    rn = tuple(float(v) for v in z["renorm"])
+    got = run_gpu(w, r, x, g, t(z["init_slot"]), t(z["init_mass"]), mask, E, t(z["pos"]), (Kw, Kr), rn, bool(ma),
+                  float(z["eps"]))
+    ref = (t(z["out_y"]).permute(0, 2, 1, 3), t(z["out_slot"]), t(z["out_mass"]))
+    check(name, got, ref, mask, dtype)
+
+
+def test_inplace_equals_functional_and_chunked_calls_carry_state():
+    B, H, U, P, T, C, K = 2, 2, 2, 8, 100, 12, (4, 6)
+    w, r, x, g, slot, mass, mask, pos = make_case(B, H, U, P, T, C, torch.float32, 9, masked=True)
+    args = dict(E=1, K=K, renorm=(0.0, 0.5), mass_aware=False, eps=1e-6)
+    full = run_gpu(w, r, x, g, slot, mass, mask, args["E"], pos, K, args["renorm"], False, 1e-6)
+    inpl = run_gpu(w, r, x, g, slot, mass, mask, args["E"], pos, K, args["renorm"], False, 1e-6, inplace=True)
+    for a, b in zip(full, inpl):
+        assert torch.equal(a, b)
+    ys, s, m = [], slot, mass
+    for lo in range(0, T, 33):
+        hi = min(T, lo + 33)
+        y, s, m = run_gpu(w[..., lo:hi], r[..., lo:hi], x[:, :, lo:hi], g[..., lo:hi], s, m, mask[:, lo:hi], args["E"],
+                          pos[:, lo:hi], K, args["renorm"], False, 1e-6)
+        ys.append(y)
+    assert torch.equal(torch.cat(ys, dim=2), full[0])
+    assert torch.equal(s, full[1]) and torch.equal(m, full[2])
+
+
+def test_all_masked_leaves_state_bit_exact():
+    B, H, U, P, T, C, K = 1, 2, 2, 4, 20, 8, (2, 2)
+    w, r, x, g, slot, mass, _, pos = make_case(B, H, U, P, T, C, torch.float32, 4)
+    mask = torch.zeros(B, T, dtype=torch.bool)
+    y, s, m = run_gpu(w, r, x, g, slot, mass, mask, 1, pos, K, (0.0, 0.0), False, 1e-6)
+    assert torch.equal(s, slot) and torch.equal(m, mass) and float(y.abs().max()) == 0.0
+
+
+def test_prefill_equals_token_by_token_decode():
+    B, H, U, P, T, C, K = 2, 4, 2, 8, 24, 16, (4, 4)
+    w, r, x, g, slot, mass, _, pos = make_case(B, H, U, P, T, C, torch.float32, 6)
+    full = run_gpu(w, r, x, g, slot, mass, None, 2, pos, K, (0.5, 0.5), True, 1e-6)
+    ops()
+    s, m = slot.clone().cuda(), mass.clone().cuda()
+    ys = []
+    for i in range(T):
+        y = torch.ops.ramnet_ops.topk_autoregressive_(
+            w[..., i].contiguous().cuda(), r[..., i].contiguous().cuda(), x[:, :, i].contiguous().cuda(),
+            g[..., i].contiguous().cuda(), s, m, torch.empty(0, dtype=torch.bool, device="cuda"), 2,
+            pos[:, i].cuda().int(), K[0], K[1], 0.5, 0.5, True, 1e-6)
+        ys.append(y.cpu())
+    tol = dict(atol=1e-4, rtol=1e-4, max_err_rate=0.01, max_q99=1.5)
+    assert_close_stats("y", torch.stack(ys, dim=2), full[0], **tol)
+    assert_close_stats("slot", s.cpu(), full[1], **tol)
+    assert_close_stats("mass", m.cpu(), full[2], **tol)
