@@ -100,7 +100,8 @@ def test_inactive_and_extreme_logits():
         assert torch.isfinite(val).all()
         assert float(val[..., :2].abs().max()) == 0.0
         assert torch.equal(idx.cpu(), ref_idx)
-        assert_close_stats("val", val.cpu(), ref_val, atol=1e-6, rtol=2e-5, max_err_rate=0.0)
+        # logits of magnitude 1000 cancel against their log-sum-exp: fp32 budget of the reference tests
+        assert_close_stats("val", val.cpu(), ref_val, **FP32_TOL)
 
 
 @pytest.mark.parametrize("shape", SHAPES[:6])
