@@ -1,0 +1,448 @@
+"""Benchmark of the RAM-Net sparse slot-memory hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload prefill|decode|addr]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input of the
+BASELINE.json shape (random logits / values of the stated distributions; no dataset is involved):
+
+  prefill (headline)  B8 T16384 H16 U2 P64 K16 C128 bf16, zero fp32 state: joined address decode
+                      + time-chunked gated sparse update/read.  tokens = B*T per step.
+  decode              B256 H16 U2 P64 K16 C128, fp32 state 8.6 GB, 1024 one-token steps.
+  addr                B8 T8192 H16 U3 P32 K8 bf16 address decode alone.
+
+At N > 1 (torchrun, one rank per GPU) every rank runs the full single-GPU shape on its own batch
+shard (weak scaling, no collective on the data path); the timed region is bracketed by a barrier
+and a device synchronise and the slowest rank's device time counts.
+
+Prints ONE JSON line.  ``value`` is whole-job tokens/s with inputs resident in HBM; ``e2e`` is the
+same metric through ``ramnet_ops.random_access_memory_attention`` with pinned HOST inputs, the
+host->device copies and the device->host copy of y inside the timed region; ``roofline`` is for the
+dominant kernel, timed with CUDA events recorded on the launch stream inside the library;
+``cpu_baseline`` is the CPU oracle (a port of the reference's algorithm) on a bounded sample.
+``--impl reference`` times that CPU port alone with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "ram-net_b200"))
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+SHAPES = {
+    "prefill": dict(B=8, T=16384, H=16, U=2, P=64, K=16, C=128, E=8),
+    "decode": dict(B=256, T=1024, H=16, U=2, P=64, K=16, C=128, E=8),
+    "addr": dict(B=8, T=8192, H=16, U=3, P=32, K=8, C=0, E=8),
+}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks sampling during the timed region
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = max(mx, float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic inputs
+# ---------------------------------------------------------------------------------------------
+def make_prefill_inputs(s, device, seed, pinned_host=False):
+    g = torch.Generator().manual_seed(seed)
+    B, T, H, U, P, C = s["B"], s["T"], s["H"], s["U"], s["P"], s["C"]
+
+    def mk(shape, fn=None):
+        out = torch.empty(shape, dtype=torch.bfloat16, pin_memory=pinned_host)
+        step = max(1, shape[0] // 8)
+        for lo in range(0, shape[0], step):  # bounded fp32 scratch
+            blk = torch.randn((min(step, shape[0] - lo),) + tuple(shape[1:]), generator=g)
+            out[lo:lo + blk.shape[0]] = (fn(blk) if fn else blk).to(torch.bfloat16)
+        return out
+
+    q = mk((B, T, H, U, P))
+    k = mk((B, T, H, U, P))
+    v = mk((B, T, H, C))
+    gamma = mk((B, T, H), lambda z: torch.sigmoid(z + 1.0))
+    host = dict(q=q, k=k, v=v, gamma=gamma)
+    if pinned_host:
+        return host
+    return {n: t.to(device) for n, t in host.items()}
+
+
+def lib():
+    import ramnet_ops._C as C
+    return C.lib
+
+
+def kernel_times(n):
+    buf = (ctypes.c_float * n)()
+    got = lib().rn_prof_read(buf, n)
+    return [buf[i] for i in range(max(got, 0))]
+
+
+# ---------------------------------------------------------------------------------------------
+# workloads (each returns a dict of measurements for this rank)
+# ---------------------------------------------------------------------------------------------
+def run_prefill(args, device, rank, barrier, max_over_ranks):
+    import ramnet_ops  # noqa: F401
+    s = SHAPES["prefill"]
+    B, T, H, U, P, K, C, E = (s[k] for k in ("B", "T", "H", "U", "P", "K", "C", "E"))
+    A = P ** U
+    dev = make_prefill_inputs(s, device, seed=rank)
+    w_view = dev["k"].permute(0, 2, 3, 4, 1)
+    r_view = dev["q"].permute(0, 2, 3, 4, 1)
+    x_view = dev["v"].permute(0, 2, 1, 3)
+    g_view = dev["gamma"].permute(0, 2, 1)
+    pos = torch.arange(T, device=device, dtype=torch.int32).view(1, T).expand(B, T).contiguous()
+    slot0 = torch.zeros(B, H, A, C, device=device)
+    mass0 = torch.full((B, H, A), 1.0 / A, device=device)
+    ops = torch.ops.ramnet_ops
+
+    def step():
+        idx, val = ops.topk_addr_forward(w_view, r_view, E, A, pos, K, K, 0.0, 0.0)
+        return ops.gsu_forward(idx, val, x_view, g_view, slot0, mass0, None, K, K, False, 1e-12)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    # per-kernel device times (events on the launch stream, recorded inside the library)
+    lib().rn_prof_enable(1)
+    t_addr, t_sched, t_apply = [], [], []
+    for _ in range(min(args.steps, 5)):
+        idx, val = ops.topk_addr_forward(w_view, r_view, E, A, pos, K, K, 0.0, 0.0)
+        t_addr += kernel_times(4)
+        ops.gsu_forward(idx, val, x_view, g_view, slot0, mass0, None, K, K, False, 1e-12)
+        ts = kernel_times(4)
+        t_sched.append(ts[0])
+        t_apply.append(ts[1])
+    lib().rn_prof_enable(0)
+    torch.cuda.synchronize()
+
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            out = step()
+        e1.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    del out
+
+    # end to end through the public API with pinned host inputs
+    import ramnet_ops as ro
+    host = make_prefill_inputs(s, device, seed=rank, pinned_host=True)
+    y_host = torch.empty((B, T, H, C), dtype=torch.bfloat16, pin_memory=True)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = y_host.numel() * y_host.element_size()
+
+    def e2e_step():
+        q, k, v, gm = (host[n].to(device, non_blocking=True) for n in ("q", "k", "v", "gamma"))
+        y, _state = ro.random_access_memory_attention(k, q, v, gm, embed_num=E, top_k=K, impl_backend="cuda")
+        y_host.copy_(y, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    torch.cuda.synchronize()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+
+    def mean(v):
+        return sum(v) / max(len(v), 1)
+
+    per_bh = T * (C * 2 + C * 2) + 2 * A * C * 4  # apply kernel: x once, y once, slot state in and out
+    step_bytes = B * H * (T * (2 * U * P * 2 + C * 2 + 2 + C * 2) + 2 * A * C * 4 + 2 * A * 4)
+    return dict(
+        tokens_per_step=B * T, ms_total=ms, steps=args.steps, e2e_ms_total=e2e_ms, e2e_steps=e2e_steps,
+        h2d=h2d, d2h=d2h, launches_per_step=3, clocks=clocks.summary(),
+        kernels={"rn_addr_fwd_kernel": mean(t_addr), "rn_gsu_schedule_kernel": mean(t_sched),
+                 "rn_gsu_apply_kernel": mean(t_apply)},
+        dominant=("rn_gsu_apply_kernel", B * H * per_bh, mean(t_apply)), step_bytes=step_bytes,
+        workload="prefill_fwd B8 T16384 H16 U2 P64(A4096) Kw16 Kr16 C128 bf16, CAPE on 8 heads, zero fp32 state")
+
+
+def run_decode(args, device, rank, barrier, max_over_ranks, steps=None):
+    import ramnet_ops  # noqa: F401
+    s = SHAPES["decode"]
+    B, H, U, P, K, C, E = (s[k] for k in ("B", "H", "U", "P", "K", "C", "E"))
+    A = P ** U
+    nsteps = steps or s["T"]
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    slot = torch.empty(B, H, A, C, device=device)
+    for b in range(0, B, 16):
+        slot[b:b + 16] = torch.randn(16, H, A, C, device=device, generator=g) * 0.1
+    mass = torch.rand(B, H, A, device=device, generator=g) + 0.1
+    nbuf = 16  # rotate through a few input sets; the 8.6 GB state is the traffic that matters
+    q = torch.randn(nbuf, B, H, U, P, device=device, generator=g).bfloat16()
+    k = torch.randn(nbuf, B, H, U, P, device=device, generator=g).bfloat16()
+    v = torch.randn(nbuf, B, H, C, device=device, generator=g).bfloat16()
+    gm = torch.sigmoid(torch.randn(nbuf, B, H, device=device, generator=g)).bfloat16()
+    pos = torch.zeros(B, device=device, dtype=torch.int32)
+    nomask = torch.empty(0, dtype=torch.bool, device=device)
+    ops = torch.ops.ramnet_ops
+
+    def one(i):
+        j = i % nbuf
+        pos.fill_(i)
+        return ops.topk_autoregressive_(k[j], q[j], v[j], gm[j], slot, mass, nomask, E, pos, K, K, 0.0, 0.0, False, 1e-12)
+
+    for i in range(8):
+        one(i)
+    torch.cuda.synchronize()
+    lib().rn_prof_enable(1)
+    tk = []
+    for i in range(8):
+        one(i)
+        tk += kernel_times(2)
+    lib().rn_prof_enable(0)
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(nsteps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    per_bh = 2 * U * P * 2 + C * 2 + 2 + 2 * K * C * 4 + 2 * K * 4 + K * C * 4 + C * 2
+    kt = sum(tk) / max(len(tk), 1)
+    return dict(tokens_per_s=B * nsteps / (ms / 1e3), ms_per_step=ms / nsteps, kernel_ms=kt,
+                kernel_gbs=B * H * per_bh / (kt / 1e3) / 1e9 if kt > 0 else None, bytes_per_step=B * H * per_bh,
+                steps=nsteps)
+
+
+def run_addr(args, device, rank, barrier, max_over_ranks):
+    import ramnet_ops  # noqa: F401
+    s = SHAPES["addr"]
+    B, T, H, U, P, K, E = (s[k] for k in ("B", "T", "H", "U", "P", "K", "E"))
+    A = P ** U
+    g = torch.Generator(device=device).manual_seed(200 + rank)
+    q = (torch.randn(B, T, H, U, P, device=device, generator=g) * 1.5).bfloat16()
+    k = (torch.randn(B, T, H, U, P, device=device, generator=g) * 1.5).bfloat16()
+    pos = torch.arange(T, device=device, dtype=torch.int32).view(1, T).expand(B, T).contiguous()
+    ops = torch.ops.ramnet_ops
+    wv, rv = k.permute(0, 2, 3, 4, 1), q.permute(0, 2, 3, 4, 1)
+    for _ in range(3):
+        ops.topk_addr_forward(wv, rv, E, A, pos, K, K, 0.0, 0.0)
+    torch.cuda.synchronize()
+    lib().rn_prof_enable(1)
+    tk = []
+    for _ in range(5):
+        ops.topk_addr_forward(wv, rv, E, A, pos, K, K, 0.0, 0.0)
+        tk += kernel_times(2)
+    lib().rn_prof_enable(0)
+    kt = sum(tk) / len(tk)
+    nbytes = B * T * H * (2 * U * P * 2 + 2 * K * 4 + 2 * K * 4)
+    return dict(tokens_per_s=B * T / (kt / 1e3), kernel_ms=kt, kernel_gbs=nbytes / (kt / 1e3) / 1e9, bytes=nbytes)
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline: the oracle port on a bounded sample of the prefill workload
+# ---------------------------------------------------------------------------------------------
+def cpu_baseline(reps=1):
+    from oracle import ramnet_oracle as orc
+    s = SHAPES["prefill"]
+    B, H, T = 1, 2, 256
+    U, P, K, C, E = s["U"], s["P"], s["K"], s["C"], 1
+    A = P ** U
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(B, T, H, U, P, generator=g).bfloat16().float().permute(0, 2, 3, 4, 1)
+    r = torch.randn(B, T, H, U, P, generator=g).bfloat16().float().permute(0, 2, 3, 4, 1)
+    x = torch.randn(B, T, H, C, generator=g).bfloat16().float().permute(0, 2, 1, 3)
+    gm = torch.sigmoid(torch.randn(B, T, H, generator=g) + 1).bfloat16().float().permute(0, 2, 1)
+    slot, mass = torch.zeros(B, H, A, C), torch.full((B, H, A), 1.0 / A)
+    pos = torch.arange(T).view(1, T)
+    best = float("inf")
+    for _ in range(reps + 1):
+        t0 = time.perf_counter()
+        orc.ram_attn(w, r, x, gm, slot, mass, None, E, pos, (K, K))
+        best = min(best, time.perf_counter() - t0)
+    # tokens carry all 16 heads in the metric; the sample ran H=2 of them
+    tokens = B * T * H / s["H"]
+    return dict(value=tokens / best, unit="tokens/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"oracle.ram_attn on B{B} H{H} T{T} U{U} P{P} K{K} C{C} fp32 (bf16-quantised inputs), "
+                       f"scaled to {s['H']}-head tokens; {best:.2f} s")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the decode and address-only measurements")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        torch.set_num_threads(os.cpu_count() or 1)
+        vals = []
+        for _ in range(max(args.warmup, 0)):
+            cpu_baseline(0)
+        for _ in range(max(1, min(args.steps, 5))):
+            vals.append(cpu_baseline(0))
+        v = sorted(x["value"] for x in vals)[len(vals) // 2]
+        base = vals[0]
+        base["value"] = v
+        line = {"impl": "reference", "metric": "prefill_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "prefill_fwd sample on host cores: " + base["sample"]},
+                "cpu_baseline": base,
+                "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the hot path has no CPU fallback)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        tns = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(tns, op=dist.ReduceOp.MAX)
+        return float(tns.item())
+
+    m = run_prefill(args, device, rank, barrier, max_over_ranks)
+    extra = {}
+    if not args.no_extra:
+        torch.cuda.empty_cache()
+        d = run_decode(args, device, rank, barrier, max_over_ranks)
+        torch.cuda.empty_cache()
+        a = run_addr(args, device, rank, barrier, max_over_ranks)
+        extra = {"decode": d, "addr": a}
+
+    peak, peak_kind = peaks()
+    name, alg_bytes, kms = m["dominant"]
+    achieved = alg_bytes / (kms / 1e3) / 1e9
+    ms_per_step = m["ms_total"] / m["steps"]
+    value = world * m["tokens_per_step"] / (ms_per_step / 1e3)
+    e2e_value = world * m["tokens_per_step"] / (m["e2e_ms_total"] / m["e2e_steps"] / 1e3)
+    line = {
+        "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": m["workload"], "io_dtype": "bf16", "state_dtype": "f32", "per_gpu_batch": SHAPES["prefill"]["B"],
+                   "l2": "inputs_exceed_l2 (1.3 GB per step)", "sharding": "batch, no data-path collective"},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
+        "gpu_launches": m["launches_per_step"] * args.steps,
+        "clocks": m["clocks"],
+        "roofline": {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kms},
+        "roofline_step": {"algorithmic_bytes": m["step_bytes"], "achieved": m["step_bytes"] / (ms_per_step / 1e3) / 1e9,
+                          "frac": m["step_bytes"] / (ms_per_step / 1e3) / 1e9 / peak},
+        "kernel_ms": m["kernels"],
+    }
+    if extra:
+        d, a = extra["decode"], extra["addr"]
+        line["decode"] = {"tokens_per_s": world * d["tokens_per_s"], "ms_per_step": d["ms_per_step"], "kernel_ms": d["kernel_ms"],
+                          "achieved_gbs": d["kernel_gbs"], "frac": None if d["kernel_gbs"] is None else d["kernel_gbs"] / peak,
+                          "algorithmic_bytes_per_step": d["bytes_per_step"], "steps": d["steps"],
+                          "workload": "decode B256 H16 U2 P64 K16 C128, fp32 state 8.6 GB"}
+        line["addr"] = {"tokens_per_s": world * a["tokens_per_s"], "kernel_ms": a["kernel_ms"], "achieved_gbs": a["kernel_gbs"],
+                        "frac": a["kernel_gbs"] / peak, "algorithmic_bytes": a["bytes"],
+                        "workload": "addr B8 T8192 H16 U3 P32 K8 bf16"}
+    if rank == 0:
+        if world == 1:
+            torch.set_num_threads(os.cpu_count() or 1)
+            line["cpu_baseline"] = cpu_baseline(1)
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

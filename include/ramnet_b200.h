@@ -35,6 +35,13 @@ const char *rn_last_error(void);
 /* Library build tag, e.g. "ramnet_b200 sm_100a". */
 const char *rn_version(void);
 
+/* Benchmark aid (no counterpart in the reference).  After rn_prof_enable(1) the calling thread's
+ * entry points record CUDA events around each of their kernel launches, on the launch stream;
+ * rn_prof_read() waits for the last event of the most recent call and writes the duration of each
+ * of its kernels in milliseconds (returns how many, -1 on a CUDA error). */
+int rn_prof_enable(int on);
+int rn_prof_read(float *ms, int n);
+
 /*
  * Address decode (Product-Softmax over U digit sub-vectors + exact Top-K prefix search +
  * CAPE cyclic shift), write and read addresses in ONE launch.

@@ -281,11 +281,14 @@ extern "C" int rn_addr_fwd(const void *w_addr, const void *r_addr, int dtype, co
     const int64_t cap = int64_t(rn_sm_count(device)) * 16;
     const int grid = int(want < cap ? want : cap);
     int rc;
+    rn_prof_reset();
+    rn_prof_mark(cudaStream_t(stream));
     if (dtype == RN_F32) rc = rn_launch_addr_fwd<float>(p, kpl, ppl, grid, cudaStream_t(stream));
     else if (dtype == RN_F16) rc = rn_launch_addr_fwd<__half>(p, kpl, ppl, grid, cudaStream_t(stream));
     else rc = rn_launch_addr_fwd<__nv_bfloat16>(p, kpl, ppl, grid, cudaStream_t(stream));
     if (rc) return rc;
     RN_CUDA(cudaGetLastError());
+    rn_prof_mark(cudaStream_t(stream));
     return 0;
 }
 

@@ -31,3 +31,38 @@ extern "C" int rn_int_bits(void) { return 32; }
 extern "C" const char *rn_last_error(void) { return g_rn_error; }
 
 extern "C" const char *rn_version(void) { return "ramnet_b200 sm_100a"; }
+
+// ------------------------------------------------------------------------------------------
+// optional per-kernel timing for benchmarks: CUDA events recorded around each launch of the
+// calling thread's next entry-point calls, on the stream the kernels run on
+// ------------------------------------------------------------------------------------------
+static thread_local bool g_prof_on = false;
+static thread_local int g_prof_count = 0;
+static thread_local cudaEvent_t g_prof_events[16];
+static thread_local int g_prof_created = 0;
+
+void rn_prof_reset() { g_prof_count = 0; }
+
+void rn_prof_mark(cudaStream_t stream) {
+    if (!g_prof_on || g_prof_count >= 16) return;
+    if (g_prof_count >= g_prof_created) {
+        if (cudaEventCreate(&g_prof_events[g_prof_created]) != cudaSuccess) return;
+        ++g_prof_created;
+    }
+    cudaEventRecord(g_prof_events[g_prof_count++], stream);
+}
+
+extern "C" int rn_prof_enable(int on) {
+    g_prof_on = on != 0;
+    g_prof_count = 0;
+    return 0;
+}
+
+extern "C" int rn_prof_read(float *ms, int n) {
+    if (g_prof_count < 2) return 0;
+    if (cudaEventSynchronize(g_prof_events[g_prof_count - 1]) != cudaSuccess) return -1;
+    int out = 0;
+    for (int i = 1; i < g_prof_count && out < n; ++i, ++out)
+        if (cudaEventElapsedTime(&ms[out], g_prof_events[i - 1], g_prof_events[i]) != cudaSuccess) return -1;
+    return out;
+}

@@ -50,6 +50,10 @@ struct RnDeviceGuard {
 
 int rn_sm_count(int device);
 
+// benchmark-only timing hooks (no-ops unless rn_prof_enable(1) was called on this thread)
+void rn_prof_reset();
+void rn_prof_mark(cudaStream_t stream);
+
 // ------------------------------------------------------------------------------------------
 // device helpers
 // ------------------------------------------------------------------------------------------

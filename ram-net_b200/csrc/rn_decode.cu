@@ -249,10 +249,13 @@ extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void
     const size_t smem = size_t(C) * (1 + RN_DEC_WARPS) * sizeof(float);
     const int grid = int(B * H);
     int rc;
+    rn_prof_reset();
+    rn_prof_mark(cudaStream_t(stream));
     if (dtype == RN_F32) rc = rn_launch_decode<float>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
     else if (dtype == RN_F16) rc = rn_launch_decode<__half>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
     else rc = rn_launch_decode<__nv_bfloat16>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
     if (rc) return rc;
     RN_CUDA(cudaGetLastError());
+    rn_prof_mark(cudaStream_t(stream));
     return 0;
 }

@@ -410,6 +410,8 @@ extern "C" int64_t rn_gsu_workspace_bytes(int64_t B, int64_t H, int64_t T, int64
 template <typename T>
 static int rn_launch_gsu(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int bh = p.B * p.H;
+    rn_prof_reset();
+    rn_prof_mark(stream);
     if (pl.smem_tables) {
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_schedule_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(pl.sched_smem)));
@@ -420,10 +422,12 @@ static int rn_launch_gsu(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t
         rn_gsu_schedule_kernel<T, false><<<bh, RN_GSU_THREADS, pl.sched_smem, stream>>>(p);
     }
     RN_CUDA(cudaGetLastError());
+    rn_prof_mark(stream);
     RN_CUDA(cudaFuncSetAttribute(rn_gsu_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  int(pl.apply_smem)));
     rn_gsu_apply_kernel<T><<<bh * pl.nslices, RN_GSU_THREADS, pl.apply_smem, stream>>>(p);
     RN_CUDA(cudaGetLastError());
+    rn_prof_mark(stream);
     return 0;
 }
 

@@ -44,6 +44,9 @@ lib.rn_gsu_fwd.restype = ctypes.c_int
 lib.rn_gsu_fwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _i64p, _i32, _ptr, _i64p, _ptr, _ptr, _ptr, _ptr, _ptr,
                            _i64p, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _f64, _i32, _ptr]
 
+lib.rn_prof_enable.argtypes = [_i32]
+lib.rn_prof_read.argtypes = [ctypes.POINTER(ctypes.c_float), _i32]
+
 INT_BITS: int = int(lib.rn_int_bits())
 
 DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}

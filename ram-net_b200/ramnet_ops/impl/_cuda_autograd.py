@@ -1,0 +1,117 @@
+"""Fake (meta) kernels and autograd formulas of the ``ramnet_ops`` operators.
+
+Same conventions as the reference's ``packages/ramnet-ops/src/ramnet_ops/impl/_cuda_autograd.py``:
+indices are non-differentiable, missing upstream gradients are not materialised, read-weight
+gradients exchanged between the update operator and the address operator are w.r.t. the POSITIVE
+weight although the joined decode stores reads negated.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def _token_major(like, B, H, K, T, dtype):
+    return like.new_empty((B, T, H, K), dtype=dtype).permute(0, 2, 3, 1)
+
+
+# ---------------------------------------------------------------------------- address decode
+@torch.library.register_fake("ramnet_ops::topk_addr_single_forward")
+def _(addr, embed_num, A, position_ids, top_k, top_k_re_norm, addr_val_neg=False, encode_batch_idx=True):
+    B, H, _, _, T = addr.shape
+    return _token_major(addr, B, H, top_k, T, torch.int32), _token_major(addr, B, H, top_k, T, torch.float32)
+
+
+@torch.library.register_fake("ramnet_ops::topk_addr_single_backward")
+def _(idx, val, addr, D_val, embed_num, position_ids, top_k, top_k_re_norm, addr_val_neg, shape, dtype):
+    B, H, U, P, _, T = shape
+    return val.new_empty((B, T, H, U, P), dtype=dtype).permute(0, 2, 3, 4, 1)
+
+
+def _single_setup(ctx, inputs, output):
+    addr, embed_num, A, position_ids, top_k, top_k_re_norm, addr_val_neg, _ = inputs
+    idx, val = output
+    B, H, U, P, T = addr.shape
+    ctx.opts = (embed_num, top_k, top_k_re_norm, addr_val_neg, (B, H, U, P, A, T), addr.dtype)
+    ctx.save_for_backward(idx, val, position_ids, addr)
+    ctx.mark_non_differentiable(idx)
+    ctx.set_materialize_grads(False)
+
+
+def _single_backward(ctx, D_idx, D_val):
+    if D_val is None:
+        return (None,) * 8
+    idx, val, position_ids, addr = ctx.saved_tensors
+    embed_num, top_k, rho, neg, shape, dtype = ctx.opts
+    d_addr = torch.ops.ramnet_ops.topk_addr_single_backward(idx, val, addr, D_val, embed_num, position_ids, top_k, rho,
+                                                            neg, shape, dtype)
+    return (d_addr,) + (None,) * 7
+
+
+torch.library.register_autograd("ramnet_ops::topk_addr_single_forward", _single_backward, setup_context=_single_setup)
+
+
+@torch.library.register_fake("ramnet_ops::topk_addr_forward")
+def _(w_addr, r_addr, embed_num, A, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm, encode_batch_idx=True):
+    B, H, _, _, T = w_addr.shape
+    K = w_top_k + r_top_k
+    return _token_major(w_addr, B, H, K, T, torch.int32), _token_major(w_addr, B, H, K, T, torch.float32)
+
+
+@torch.library.register_fake("ramnet_ops::topk_addr_backward")
+def _(idx, val, w_addr, r_addr, D_val, embed_num, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm, shape, dtype):
+    B, H, U, P, _, T = shape
+    make = lambda: val.new_empty((B, T, H, U, P), dtype=dtype).permute(0, 2, 3, 4, 1)  # noqa: E731
+    return make(), make()
+
+
+def _joined_setup(ctx, inputs, output):
+    w_addr, r_addr, embed_num, A, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm, _ = inputs
+    idx, val = output
+    B, H, U, P, T = w_addr.shape
+    ctx.opts = (embed_num, w_top_k, r_top_k, w_re_norm, r_re_norm, (B, H, U, P, A, T), w_addr.dtype)
+    ctx.save_for_backward(idx, val, position_ids, w_addr, r_addr)
+    ctx.mark_non_differentiable(idx)
+    ctx.set_materialize_grads(False)
+
+
+def _joined_backward(ctx, D_idx, D_val):
+    if D_val is None:
+        return (None,) * 10
+    idx, val, position_ids, w_addr, r_addr = ctx.saved_tensors
+    embed_num, w_k, r_k, w_rho, r_rho, shape, dtype = ctx.opts
+    d_w, d_r = torch.ops.ramnet_ops.topk_addr_backward(idx, val, w_addr, r_addr, D_val, embed_num, position_ids, w_k,
+                                                       r_k, w_rho, r_rho, shape, dtype)
+    return (d_w if ctx.needs_input_grad[0] else None, d_r if ctx.needs_input_grad[1] else None) + (None,) * 8
+
+
+torch.library.register_autograd("ramnet_ops::topk_addr_forward", _joined_backward, setup_context=_joined_setup)
+
+
+# ---------------------------------------------------------------------------- decode step
+@torch.library.register_fake("ramnet_ops::topk_autoregressive_")
+def _(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm,
+      mass_aware, eps):
+    return x.new_empty(x.shape)
+
+
+@torch.library.register_fake("ramnet_ops::decode_fused_")
+def _(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm,
+      mass_aware, eps, norm_weight, gate_logits, norm_eps):
+    return x.new_empty(x.shape)
+
+
+# ---------------------------------------------------------------------------- prefill update / read
+def _y_like(x):
+    B, H, T, C = x.shape
+    return x.new_empty((B, T, H, C)).permute(0, 2, 1, 3)
+
+
+@torch.library.register_fake("ramnet_ops::gsu_forward")
+def _(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, w_top_k, r_top_k, mass_aware, eps):
+    return (_y_like(x), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
+            init_mass.new_empty(init_mass.shape, dtype=torch.float32))
+
+
+@torch.library.register_fake("ramnet_ops::gsu_forward_")
+def _(addr_idx, addr_val, x, gamma, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps):
+    return _y_like(x)
