@@ -140,6 +140,34 @@ int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *idx_strides,
                int64_t workspace_bytes, int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw,
                int64_t Kr, int mass_aware, double eps, int device, void *stream);
 
+/*
+ * Prefill update without any allocation (no counterpart in the reference, which allocates its
+ * event buffers with the framework allocator inside the operator).
+ *
+ * Same computation, arguments and results as rn_gsu_fwd, minus the workspace: the event schedule
+ * is kept in a fixed array compiled into the library (rn_gsu_static_scratch_bytes() bytes of
+ * device memory on every GPU that loads the library, held until the process exits).  Meant for
+ * callers that cannot allocate device memory where they call from: an allocator or memory-pool
+ * callback, a serving loop that sized its pools up front, a plugin whose host owns all device
+ * memory.  The function calls no cudaMalloc / cudaFree nor any allocating library routine.
+ *
+ *  - Shapes whose schedule does not fit the array are rejected with a non-zero return and a
+ *    message (nothing is launched); shorter calls with state carry-over give the same result.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ *    caches it; make that first call outside any stream capture.
+ *  - All calls on one device share the array and it keeps the previous call's contents.  Nothing
+ *    in it has to start at zero (each call rewrites every entry it later reads), but two calls
+ *    that overlap on the GPU (different streams, or different host threads without ordering) race
+ *    on it: keep calls on one stream or order them with events.
+ */
+int64_t rn_gsu_static_scratch_bytes(void);
+int rn_gsu_fwd_static(const int32_t *idx, const float *val, const int64_t *idx_strides, const void *x,
+                      const int64_t *x_strides, const void *gamma, const int64_t *gamma_strides, int dtype,
+                      const uint8_t *mask, const int64_t *mask_strides, const float *slot_in, const float *mass_in,
+                      float *slot_out, float *mass_out, void *y, const int64_t *y_strides,
+                      int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
+                      int mass_aware, double eps, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -484,3 +484,62 @@ extern "C" int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *i
     if (dtype == RN_F16) return rn_launch_gsu<__half>(p, pl, stream);
     return rn_launch_gsu<__nv_bfloat16>(p, pl, stream);
 }
+
+// ------------------------------------------------------------------------------------------
+// rn_gsu_fwd_static: the same prefill update for callers that must not allocate
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library cannot hand over a workspace: code running inside a region where
+// device allocation is forbidden or would deadlock (an allocator callback, a real-time serving
+// loop that pre-sized its pools, a plugin whose host owns all device memory and exposes no
+// allocator).  For them the event schedule that rn_gsu_fwd keeps in a caller workspace lives in
+// one fixed array inside the library image instead.  The array is part of the module, so every
+// GPU that loads the library keeps RN_STATIC_SCRATCH_BYTES of device memory until the process
+// exits; that is why the limit is small.
+constexpr size_t RN_STATIC_SCRATCH_BYTES = size_t(32) << 20;  // 32 MiB
+static __device__ __align__(256) unsigned char rn_static_scratch[RN_STATIC_SCRATCH_BYTES];
+
+#include <mutex>
+
+// In host code `rn_static_scratch` is only a handle for the runtime, not a device address; the
+// address the kernels need comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+static int rn_static_scratch_ptr(int device, void **out) {
+    static std::mutex mu;
+    static void *cached[64] = {nullptr};
+    RN_REQUIRE(device >= 0 && device < 64, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[device] == nullptr) {
+        void *ptr = nullptr;
+        RN_CUDA(cudaGetSymbolAddress(&ptr, rn_static_scratch));
+        RN_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address");
+        cached[device] = ptr;
+    }
+    *out = cached[device];
+    return 0;
+}
+
+extern "C" int64_t rn_gsu_static_scratch_bytes(void) { return int64_t(RN_STATIC_SCRATCH_BYTES); }
+
+extern "C" int rn_gsu_fwd_static(const int32_t *idx, const float *val, const int64_t *idx_strides, const void *x,
+                                 const int64_t *x_strides, const void *gamma, const int64_t *gamma_strides, int dtype,
+                                 const uint8_t *mask, const int64_t *mask_strides, const float *slot_in,
+                                 const float *mass_in, float *slot_out, float *mass_out, void *y,
+                                 const int64_t *y_strides, int64_t B, int64_t H, int64_t T, int64_t A, int64_t C,
+                                 int64_t Kw, int64_t Kr, int mass_aware, double eps, int device, void *stream) {
+    rn_clear_error();
+    RnGsuPlan pl;
+    if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return rc;
+    RN_REQUIRE(pl.total <= RN_STATIC_SCRATCH_BYTES,
+               "rn_gsu_fwd_static: this shape needs %lld bytes of schedule scratch but the built-in array holds %lld; "
+               "split the sequence into shorter calls (state carries over) or use rn_gsu_fwd with a workspace",
+               (long long)pl.total, (long long)RN_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    {
+        RnDeviceGuard guard(device);
+        RN_REQUIRE(guard.ok, "cannot make device %d current", device);
+        if (int rc = rn_static_scratch_ptr(device, &scratch)) return rc;
+    }
+    return rn_gsu_fwd(idx, val, idx_strides, x, x_strides, gamma, gamma_strides, dtype, mask, mask_strides, slot_in,
+                      mass_in, slot_out, mass_out, y, y_strides, scratch, int64_t(RN_STATIC_SCRATCH_BYTES), B, H, T, A, C,
+                      Kw, Kr, mass_aware, eps, device, stream);
+}
