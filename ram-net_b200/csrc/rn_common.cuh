@@ -69,6 +69,36 @@ template <> __device__ __forceinline__ float rn_from_float<float>(float v) { ret
 template <> __device__ __forceinline__ __half rn_from_float<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 rn_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// 4 consecutive elements <-> float4; pointers must be aligned to 4 elements
+template <typename T> __device__ __forceinline__ float4 rn_load4(const T *p);
+template <> __device__ __forceinline__ float4 rn_load4<float>(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+template <> __device__ __forceinline__ float4 rn_load4<__half>(const __half *p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <> __device__ __forceinline__ float4 rn_load4<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void rn_store4(T *p, float4 v);
+template <> __device__ __forceinline__ void rn_store4<float>(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+template <> __device__ __forceinline__ void rn_store4<__half>(__half *p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__half2 *>(&raw.x) = __floats2half2_rn(v.x, v.y);
+    *reinterpret_cast<__half2 *>(&raw.y) = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+template <> __device__ __forceinline__ void rn_store4<__nv_bfloat16>(__nv_bfloat16 *p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
 // Monotone map float -> uint32 (larger float => larger integer); -0.0 must be canonicalised
 // by the caller (x + 0.0f) so that it ties with +0.0.
 __device__ __forceinline__ uint32_t rn_ord(float f) {

@@ -4,28 +4,45 @@
 // or one read of one slot) gets a ROUND number: the count of earlier live events of the same
 // chunk on the same slot (writes of a token come before its reads).  Events of one round touch
 // pairwise different slots, so a round is applied by all threads in parallel with no atomics;
-// rounds are separated by CTA barriers.  Two kernels:
+// rounds are separated by barriers.  Two kernels:
 //
 //   schedule (one CTA per (b,h), chunks in order):   rounds, the mass recurrence and the gain
-//       of every write, the (mass-aware) coefficient of every read -> per-chunk event lists
-//       sorted by round.  Channel independent, so done once per (b,h).
+//       of every write, the (mass-aware) coefficient of every read -> one record per chunk with
+//       the events sorted by round.  Channel independent, so done once per (b,h).
 //   apply (one CTA per (b,h, channel slice)):   the slice [A][cs] of the slot state stays in
-//       shared memory for the whole sequence; per chunk it stages the x tile, applies the
-//       rounds (row update / row read into a per-(token,k) buffer), reduces the reads over k in a
-//       fixed order and stores y.  Deterministic: no floating-point atomics anywhere.
+//       shared memory for the whole sequence; the chunk records are streamed into shared memory
+//       with 1-D bulk async copies (TMA, mbarrier completion) one chunk ahead; per chunk the
+//       rounds are applied (row update / row read into a per-(token,k) buffer), the reads are
+//       reduced over k in a fixed order and y is stored.  Deterministic: no floating-point
+//       atomics anywhere.
+//
+// Chunk record (global workspace, 16-byte aligned, fixed size per call):
+//   u16 header[RN_GSU_HDR]: [0] = R (rounds), [1 + r] = first entry of round r, [1 + R] = entry count
+//   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-21 token in chunk, 22-28 k,
+//                   29 read, 30 zero-contribution read (masked or zero-weight: y += 0)
+//   f32 coef[NEp]:  gain of a write / weight of a read (mass-aware scaling folded in)
+//   u32 slot[NEp]:  only in the wide format (A > 65536)
 #pragma once
 
 #include "rn_common.cuh"
 #include "rn_gsu.cuh"
 
-constexpr int RN_GSU_THREADS = 256;
+constexpr int RN_GSU_THREADS = 256;               // schedule kernel and generic apply kernel
 constexpr int RN_GSU_LMAX = 64;                   // longest time chunk
 constexpr int RN_GSU_NE_MAX = 4096;               // most events per chunk (L * (Kw + Kr))
 constexpr int RN_GSU_RMAX = 2 * RN_GSU_LMAX;      // most rounds in a chunk
-constexpr int RN_GSU_OFFS = RN_GSU_RMAX + 4;      // per-chunk header: n_rounds, off[0 .. R+1]
+constexpr int RN_GSU_HDR = 136;                   // u16 header entries (272 bytes)
+constexpr int RN_GSU_HDR_BYTES = RN_GSU_HDR * 2;
 
-constexpr uint32_t RN_EV_READ = 1u << 16;
-constexpr uint32_t RN_EV_ZERO = 1u << 17;
+constexpr uint32_t RN_EV_READ = 1u << 29;
+constexpr uint32_t RN_EV_ZERO = 1u << 30;
+
+__host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int t, int k, bool read, bool zero) {
+    return (slot16 & 0xffffu) | (uint32_t(t) << 16) | (uint32_t(k) << 22) | (read ? RN_EV_READ : 0u) |
+           (zero ? RN_EV_ZERO : 0u);
+}
+__host__ __device__ inline int rn_ev_t(uint32_t m) { return int((m >> 16) & 63u); }
+__host__ __device__ inline int rn_ev_k(uint32_t m) { return int((m >> 22) & 127u); }
 
 struct RnGsuParams {
     // decoded addresses, logical (B,H,Kw+Kr,T)
@@ -46,17 +63,17 @@ struct RnGsuParams {
     float *slot_out;
     const float *mass_in;
     float *mass_out;
-    int B, H, T, A, C, Kw, Kr, L, nchunks, NE;
+    int B, H, T, A, C, Kw, Kr, L, nchunks, NE, NEp;
     int mass_aware;
     float eps;
     // schedule workspace
-    uint32_t *ev_slot;
-    uint32_t *ev_meta;
-    float *ev_coef;
-    uint16_t *ev_offs;
-    uint32_t *claim;  // global claim table (B*H*A) when the tables do not fit shared memory
+    int *status;              // device-side error word (0 = ok)
+    unsigned char *records;   // nchunks * B * H records of rec_bytes each
+    int64_t rec_bytes;
+    int wide;                 // records carry the separate u32 slot array
+    uint32_t *claim;          // global claim table (B*H*A) when the tables do not fit shared memory
     // apply kernel
-    int cs;           // channels per CTA (multiple of 4)
+    int cs;                   // channels per CTA (multiple of 4)
     int nslices;
     int state_in_smem;
 };
@@ -64,4 +81,42 @@ struct RnGsuParams {
 __host__ __device__ inline int rn_gsu_chunk_len(int Kw, int Kr) {
     int L = RN_GSU_NE_MAX / (Kw + Kr);
     return L > RN_GSU_LMAX ? RN_GSU_LMAX : (L < 1 ? 1 : L);
+}
+
+// ---- mbarrier / bulk-copy (TMA 1-D) primitives -----------------------------------------------
+__device__ __forceinline__ uint32_t rn_smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void rn_mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(rn_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void rn_mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void rn_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void rn_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(rn_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool rn_mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(rn_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^31 clock cycles (about a second) and reports failure.
+__device__ __forceinline__ bool rn_mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    if (rn_mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!rn_mbar_try_wait(bar, parity)) {
+        if (clock64() - start > (1ll << 31)) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void rn_bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     rn_smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(rn_smem_u32(bar))
+                 : "memory");
 }
