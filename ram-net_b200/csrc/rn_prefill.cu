@@ -11,15 +11,13 @@
 template <typename T, bool SMEM_TABLES, int EPT>
 __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const RnGsuParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ int hist[RN_GSU_RMAX + 2];
-    __shared__ int cursor[RN_GSU_RMAX + 2];
-    __shared__ float gam[RN_GSU_LMAX];
+    __shared__ float gam[2][RN_GSU_LMAX];
     __shared__ float tok_scale[RN_GSU_LMAX];
-    __shared__ unsigned char tok_live[RN_GSU_LMAX];
+    __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
 
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x;
     const int A = p.A, KT = p.Kw + p.Kr, NEp = p.NEp;
     const bool pow2 = (A & (A - 1)) == 0;
 
@@ -54,46 +52,58 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
         ev_t[j] = e / KT;
         ev_k[j] = e - ev_t[j] * KT;
     }
-    __syncthreads();
 
     const T *gamma = static_cast<const T *>(p.gamma) + b * p.gb + h * p.gh;
     const int64_t ibase = b * p.ib + h * p.ih;
 
+    // software pipeline: the raw idx / val of the next chunk are loaded while this one is resolved
+    int nraw[EPT];
+    float nval[EPT];
+    auto prefetch = [&](int chunk) {
+        const int t0 = chunk * p.L;
+        const int Lc = min(p.L, p.T - t0);
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            nraw[j] = 0;
+            nval[j] = 0.f;
+            if (chunk < p.nchunks && ev_t[j] < Lc) {
+                const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
+                nraw[j] = p.idx[o];
+                nval[j] = p.val[o];
+            }
+        }
+        if (chunk < p.nchunks && tid < Lc) {
+            gam[chunk & 1][tid] = rn_to_float<T>(gamma[(t0 + tid) * p.gt]);
+            tok_live[chunk & 1][tid] = p.mask ? p.mask[b * p.mb + (t0 + tid) * p.mt] : 1;
+        }
+    };
+    prefetch(0);
+    __syncthreads();
+
     for (int chunk = 0; chunk < p.nchunks; ++chunk) {
         const int t0 = chunk * p.L;
         const int Lc = min(p.L, p.T - t0);
+        const float *g_cur = gam[chunk & 1];
+        const unsigned char *live_cur = tok_live[chunk & 1];
 
-        if (tid < Lc) {
-            gam[tid] = rn_to_float<T>(gamma[(t0 + tid) * p.gt]);
-            tok_live[tid] = p.mask ? p.mask[b * p.mb + (t0 + tid) * p.mt] : 1;
-        }
-        // ---- stage this thread's events -------------------------------------------------------
+        // ---- this thread's events ---------------------------------------------------------------
         uint32_t ea[EPT];
         float ev[EPT], ec[EPT];
-        int er[EPT];          // round, or -1 dead write, -2 dead read, -3 out of range
+        int er[EPT];          // round, or -1 dead (zero weight / masked token), -3 out of range
         uint32_t pend = 0;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             er[j] = -3;
-            ea[j] = 0;
-            ev[j] = 0.f;
             ec[j] = 0.f;
+            ea[j] = pow2 ? uint32_t(nraw[j] & (A - 1)) : uint32_t(nraw[j] % A);
+            ev[j] = fabsf(nval[j]);
             if (ev_t[j] < Lc) {
-                const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
-                const int raw = p.idx[o];
-                ea[j] = pow2 ? uint32_t(raw & (A - 1)) : uint32_t(raw % A);
-                ev[j] = fabsf(p.val[o]);
-            }
-        }
-        __syncthreads();  // gam / tok_live visible
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            if (ev_t[j] < Lc) {
-                const bool live = tok_live[ev_t[j]] && ev[j] != 0.f;
-                er[j] = live ? 0 : (ev_k[j] < p.Kw ? -1 : -2);
+                const bool live = live_cur[ev_t[j]] && ev[j] != 0.f;
+                er[j] = live ? 0 : -1;
                 if (live) pend |= 1u << j;
             }
         }
+        prefetch(chunk + 1);
 
         // ---- rounds: the earliest pending event of each slot wins, is processed and retires ----
         int R = 0;
@@ -107,7 +117,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
                 if (!(pend & (1u << j))) continue;
                 if (claim[ea[j]] == uint32_t(j * RN_GSU_THREADS + tid)) {
                     if (ev_k[j] < p.Kw) {
-                        const RnGate g = rn_gate(ev[j], gam[ev_t[j]], mass[ea[j]], p.eps);
+                        const RnGate g = rn_gate(ev[j], g_cur[ev_t[j]], mass[ea[j]], p.eps);
                         mass[ea[j]] = g.mass;
                         ec[j] = g.gain;
                     } else {
@@ -147,55 +157,23 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
                 if (ev_t[j] < Lc && ev_k[j] >= p.Kw && er[j] >= 0) ec[j] *= tok_scale[ev_t[j]];
         }
 
-        // ---- counting sort by round (dead reads ride in round 0 with the zero flag) ---------------
-        for (int r = tid; r < R + 2; r += RN_GSU_THREADS) hist[r] = 0;
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            const bool emit = er[j] >= 0 || er[j] == -2;
-            const int list = er[j] >= 0 ? er[j] : 0;
-            const unsigned act = __ballot_sync(RN_FULL, emit);
-            if (emit) {
-                const unsigned grp = __match_any_sync(act, list);
-                if (lane == __ffs(grp) - 1) atomicAdd(&hist[list + 1], __popc(grp));
-            }
-        }
-        __syncthreads();
-        if (tid == 0) {
-            int acc = 0;
-            for (int r = 0; r <= R; ++r) {
-                acc += hist[r];
-                hist[r] = acc;  // first entry of round r; hist[R] = entry count
-                cursor[r] = acc;
-            }
-        }
-        __syncthreads();
+        // ---- the chunk record, in event order (coalesced) ------------------------------------------
         unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
-        uint16_t *o_hdr = reinterpret_cast<uint16_t *>(rec);
         uint32_t *o_meta = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES);
         float *o_coef = reinterpret_cast<float *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 4);
         uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            const bool emit = er[j] >= 0 || er[j] == -2;
-            const int list = er[j] >= 0 ? er[j] : 0;
-            const unsigned act = __ballot_sync(RN_FULL, emit);
-            if (emit) {
-                const unsigned grp = __match_any_sync(act, list);
-                const int leader = __ffs(grp) - 1;
-                int base = 0;
-                if (lane == leader) base = atomicAdd(&cursor[list], __popc(grp));
-                base = __shfl_sync(grp, base, leader);
-                const int pos = base + __popc(grp & ((1u << lane) - 1u));
-                const bool read = ev_k[j] >= p.Kw;
-                o_meta[pos] = rn_ev_pack(ea[j], ev_t[j], read ? ev_k[j] - p.Kw : ev_k[j], read, er[j] < 0);
-                o_coef[pos] = er[j] >= 0 ? ec[j] : 0.f;
-                if (p.wide) o_slot[pos] = ea[j];
+            const int e = j * RN_GSU_THREADS + tid;
+            if (e < NEp) {
+                const bool dead = er[j] < 0;
+                o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead);
+                o_coef[e] = dead ? 0.f : ec[j];
+                if (p.wide) o_slot[e] = ea[j];
             }
         }
-        if (tid == 0) o_hdr[0] = uint16_t(R);
-        for (int r = tid; r <= R; r += RN_GSU_THREADS) o_hdr[1 + r] = uint16_t(hist[r]);
-        __syncthreads();
+        if (tid == 0) *reinterpret_cast<uint32_t *>(rec) = uint32_t(R);
+        __syncthreads();  // gam / tok_live of the next chunk are complete; ev_v / ev_c may be reused
     }
 
     if (SMEM_TABLES) {
@@ -205,12 +183,12 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
 }
 
 // ------------------------------------------------------------------------------------------
-// generic apply kernel: any C, state in shared or global memory, records read from global
+// generic apply kernel: any C, state in shared or global memory, records read from global.
+// Each round scans the whole record; reads go through a per-(token,k) buffer.
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGsuParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ int offs[RN_GSU_HDR];
 
     const int slice = blockIdx.x % p.nslices;
     const int bh = blockIdx.x / p.nslices;
@@ -219,7 +197,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
     const int cs = p.cs, G = cs >> 2, C = p.C, A = p.A;
     const int c0 = slice * cs;
     const int cvalid = min(cs, C - c0);
-    const int Kr = p.Kr;
+    const int Kw = p.Kw, Kr = p.Kr, KT = Kw + Kr;
 
     // dynamic smem: [S A*cs] (state_in_smem) | xt[L*cs] | yk[L*Kr*cs]
     float *cur = reinterpret_cast<float *>(dyn);
@@ -249,14 +227,13 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
     for (int chunk = 0; chunk < p.nchunks; ++chunk) {
         const int t0 = chunk * p.L;
         const int Lc = min(p.L, p.T - t0);
+        const int ne = Lc * KT;
         const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
-        const uint16_t *e_hdr = reinterpret_cast<const uint16_t *>(rec);
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
         const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
+        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
 
-        const int R = e_hdr[0];
-        for (int i = tid; i <= R; i += RN_GSU_THREADS) offs[i] = e_hdr[1 + i];
         for (int i = tid; i < Lc * cs; i += RN_GSU_THREADS) {
             const int t = i / cs, c = i - t * cs;
             xt[i] = c < cvalid ? rn_to_float<T>(x[int64_t(t0 + t) * p.xt + c]) : 0.f;
@@ -264,20 +241,23 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
         __syncthreads();
 
         for (int r = 0; r < R; ++r) {
-            const int beg = offs[r], end = offs[r + 1];
-            for (int i = beg * G + tid; i < end * G; i += RN_GSU_THREADS) {
+            for (int i = tid; i < ne * G; i += RN_GSU_THREADS) {
                 const int ev = i / G, sub = i - ev * G;
                 const uint32_t meta = e_meta[ev];
+                const int t = ev / KT, k = ev - t * KT;
+                const bool dead = (meta & RN_EV_DEAD) != 0;
+                if (dead ? (r != 0 || k < Kw) : rn_ev_round(meta) != r) continue;
+                float *dst = yk + (t * Kr + (k - Kw)) * cs + sub * 4;
+                if (dead) {  // a no-op read contributes zero
+                    dst[0] = dst[1] = dst[2] = dst[3] = 0.f;
+                    continue;
+                }
                 const uint32_t a = p.wide ? e_slot[ev] : (meta & 0xffffu);
                 const float coef = e_coef[ev];
-                const int t = rn_ev_t(meta), k = rn_ev_k(meta);
                 float *row = S + int64_t(a) * srow + sub * 4;
-                float *dst = yk + (t * Kr + k) * cs + sub * 4;
-                if (meta & RN_EV_ZERO) {
-                    dst[0] = dst[1] = dst[2] = dst[3] = 0.f;
-                } else if (vec) {
+                if (vec) {
                     float4 s = *reinterpret_cast<float4 *>(row);
-                    if (meta & RN_EV_READ) {
+                    if (k >= Kw) {
                         s.x *= coef; s.y *= coef; s.z *= coef; s.w *= coef;
                         *reinterpret_cast<float4 *>(dst) = s;
                     } else {
@@ -291,7 +271,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
                 } else {
                     const int nc = min(4, cvalid - sub * 4);
                     for (int j = 0; j < nc; ++j) {
-                        if (meta & RN_EV_READ) dst[j] = coef * row[j];
+                        if (k >= Kw) dst[j] = coef * row[j];
                         else row[j] = fmaf(coef, xt[t * cs + sub * 4 + j] - row[j], row[j]);
                     }
                 }
@@ -328,69 +308,44 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
 }
 
 // ------------------------------------------------------------------------------------------
-// fast apply kernel: C % 4 == 0, A <= 65536, slice state + streamed chunk records in shared memory
+// fast apply kernel: C % 4 == 0, A <= 65536; slice state + streamed chunk records in shared memory.
+//
+// Token-major: the CTA's 512 threads are split into one group per token of the chunk; inside a
+// group, thread (q, sub) owns the events k = q, q + KL, ... of that token for the 4 channels
+// sub*4 .. sub*4+3 and keeps their (meta, coefficient) in registers for the whole chunk.  x[t] sits
+// in registers (prefetched one chunk ahead), the token's output accumulates in registers and is
+// combined across the group's k-lanes with shuffles in a fixed order: the only shared-memory
+// traffic per event is the slot row itself.  One CTA barrier per round.
 // ------------------------------------------------------------------------------------------
 constexpr int RN_APPLY_THREADS = 512;
 
-template <int CS>
-__device__ __forceinline__ void rn_apply_entry(const uint32_t meta, const float coef, float *__restrict__ S,
-                                               const float *__restrict__ xt, float *__restrict__ yk, const int Kr,
-                                               const int sub) {
-    // one thread handles CPT = min(CS, 8) channels of one event, starting at channel sub * CPT
-    constexpr int CPT = CS >= 8 ? 8 : 4;
-    const int t = rn_ev_t(meta), k = rn_ev_k(meta);
-    float *dst = yk + (t * Kr + k) * CS + sub * CPT;
-    if (meta & RN_EV_ZERO) {
-#pragma unroll
-        for (int v = 0; v < CPT / 4; ++v) reinterpret_cast<float4 *>(dst)[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-        return;
-    }
-    float *row = S + (meta & 0xffffu) * CS + sub * CPT;
-    if (meta & RN_EV_READ) {
-#pragma unroll
-        for (int v = 0; v < CPT / 4; ++v) {
-            float4 s = reinterpret_cast<const float4 *>(row)[v];
-            s.x *= coef; s.y *= coef; s.z *= coef; s.w *= coef;
-            reinterpret_cast<float4 *>(dst)[v] = s;
-        }
-    } else {
-        const float *xr = xt + t * CS + sub * CPT;
-#pragma unroll
-        for (int v = 0; v < CPT / 4; ++v) {
-            float4 s = reinterpret_cast<const float4 *>(row)[v];
-            const float4 xv = reinterpret_cast<const float4 *>(xr)[v];
-            s.x = fmaf(coef, xv.x - s.x, s.x);
-            s.y = fmaf(coef, xv.y - s.y, s.y);
-            s.z = fmaf(coef, xv.z - s.z, s.z);
-            s.w = fmaf(coef, xv.w - s.w, s.w);
-            reinterpret_cast<float4 *>(row)[v] = s;
-        }
-    }
-}
-
-template <typename T, int CS>
-__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p) {
-    constexpr int CPT = CS >= 8 ? 8 : 4;   // channels per thread per event
-    constexpr int G = CS / CPT;            // threads per event
-    constexpr int G4 = CS / 4;             // float4 groups per row
+template <typename T, int CS, int EV>
+__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2) {
+    constexpr int G = CS / 4;  // threads per event (one float4 of channels each)
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ __align__(8) uint64_t mbar[2];
 
     const int slice = blockIdx.x % p.nslices;
     const int bh = blockIdx.x / p.nslices;
     const int b = bh / p.H, h = bh % p.H;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int C = p.C, A = p.A, Kr = p.Kr, L = p.L;
+    const int tid = threadIdx.x;
+    const int C = p.C, A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, L = p.L;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);  // multiple of 4
     const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);  // header + meta + coef
 
-    // dynamic smem: rec[2][rec_copy] | S[A*CS] | yk[L*Kr*CS] | xt[2][L*CS]
+    // thread -> (token of the chunk, k-lane, channel group)
+    const int TPT = 1 << tpt_log2;          // threads per token (8, 16 or 32: a group never leaves its warp)
+    const int KL = TPT / G;                 // k-lanes per token
+    const int tok = tid >> tpt_log2;
+    const int w = tid & (TPT - 1);
+    const int sub = w % G, q = w / G;
+    const bool chan_ok = sub * 4 < cvalid;
+
+    // dynamic smem: rec[2][rec_stride] | S[A*CS]
     const size_t rec_stride = (size_t(rec_copy) + 127) / 128 * 128;
     unsigned char *rec0 = dyn;
     float *S = reinterpret_cast<float *>(dyn + 2 * rec_stride);
-    float *yk = S + size_t(A) * CS;
-    float *xt0 = yk + size_t(L) * Kr * CS;
 
     if (tid == 0) {
         rn_mbar_init(&mbar[0], 1);
@@ -407,42 +362,23 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     // state slice -> shared memory
     {
         const float *src = p.slot_in + int64_t(bh) * A * C + c0;
-        for (int i = tid; i < A * G4; i += RN_APPLY_THREADS) {
-            const int a = i / G4, sub = i - a * G4;
+        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
+            const int a = i / G, sg = i - a * G;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (sub * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sub * 4);
-            *reinterpret_cast<float4 *>(S + a * CS + sub * 4) = v;
+            if (sg * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sg * 4);
+            *reinterpret_cast<float4 *>(S + a * CS + sg * 4) = v;
         }
     }
-    const T *x = static_cast<const T *>(p.x) + b * p.xb + h * p.xh + c0;
-    T *y = static_cast<T *>(p.y) + b * p.yb + h * p.yh + c0;
+    const T *x = static_cast<const T *>(p.x) + b * p.xb + h * p.xh + c0 + sub * 4;
+    T *y = static_cast<T *>(p.y) + b * p.yb + h * p.yh + c0 + sub * 4;
 
-    // x tile of chunk 0 (threads cover (t, 4-channel group) pairs; L*G4 <= 64*32 = 2048 -> up to 4 per thread)
-    constexpr int XPT = (RN_GSU_LMAX * G4 + RN_APPLY_THREADS - 1) / RN_APPLY_THREADS;
-    float4 xreg[XPT];
     auto load_x = [&](int chunk) {
-        const int t0 = chunk * L;
-        const int Lc = min(L, p.T - t0);
-#pragma unroll
-        for (int q = 0; q < XPT; ++q) {
-            const int i = q * RN_APPLY_THREADS + tid;
-            const int t = i / G4, sub = i - t * G4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < Lc && sub * 4 < cvalid) {
-                v = rn_load4<T>(x + int64_t(t0 + t) * p.xt + sub * 4);
-            }
-            xreg[q] = v;
-        }
+        const int t = chunk * L + tok;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (chunk < p.nchunks && tok < L && t < p.T && chan_ok) v = rn_load4<T>(x + int64_t(t) * p.xt);
+        return v;
     };
-    auto store_x = [&](float *xt) {
-#pragma unroll
-        for (int q = 0; q < XPT; ++q) {
-            const int i = q * RN_APPLY_THREADS + tid;
-            if (i < L * G4) *reinterpret_cast<float4 *>(xt + i * 4) = xreg[q];
-        }
-    };
-    load_x(0);
-    store_x(xt0);
+    float4 xnext = load_x(0);
     __syncthreads();
 
     bool failed = false;
@@ -451,78 +387,84 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
         const int t0 = chunk * L;
         const int Lc = min(L, p.T - t0);
         const bool more = chunk + 1 < p.nchunks;
-        // prefetch the next chunk: its record by bulk copy, its x tile into registers
-        if (more) {
-            if (tid == 0) {
-                rn_fence_proxy_async();
-                rn_mbar_expect_tx(&mbar[buf ^ 1], rec_copy);
-                rn_bulk_g2s(rec0 + (buf ^ 1) * rec_stride, records + int64_t(chunk + 1) * p.rec_bytes, rec_copy,
-                            &mbar[buf ^ 1]);
-            }
-            load_x(chunk + 1);
+        const float4 xv = xnext;
+        // prefetch the next chunk: its record by bulk copy, its x row into registers
+        if (more && tid == 0) {
+            rn_fence_proxy_async();
+            rn_mbar_expect_tx(&mbar[buf ^ 1], rec_copy);
+            rn_bulk_g2s(rec0 + (buf ^ 1) * rec_stride, records + int64_t(chunk + 1) * p.rec_bytes, rec_copy,
+                        &mbar[buf ^ 1]);
         }
+        xnext = load_x(chunk + 1);
         if (!rn_mbar_wait_bounded(&mbar[buf], (chunk >> 1) & 1)) failed = true;
         if (__syncthreads_or(failed)) {
             // a bulk copy never completed: record it, give the copy in flight a last bounded chance
-            // to land (it targets this CTA's shared memory), and leave without touching the outputs
+            // to land (it targets this CTA's shared memory), and leave
             if (tid == 0) atomicExch(p.status, 1);
             if (more) rn_mbar_wait_bounded(&mbar[buf ^ 1], ((chunk + 1) >> 1) & 1);
             return;
         }
 
         const unsigned char *rec = rec0 + buf * rec_stride;
-        const uint16_t *hdr = reinterpret_cast<const uint16_t *>(rec);
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const float *xt = xt0 + buf * (L * CS);
-        const int R = hdr[0];
+        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
 
-        // rounds 0 and 1 on the whole CTA, the sparse later rounds on warp 0 alone
-        const int wide_rounds = min(R, 2);
-        for (int r = 0; r < wide_rounds; ++r) {
-            const int beg = hdr[1 + r], end = hdr[2 + r];
-            for (int i = beg * G + tid; i < end * G; i += RN_APPLY_THREADS) {
-                const int ev = i / G, sub = i - ev * G;
-                rn_apply_entry<CS>(e_meta[ev], e_coef[ev], S, xt, yk, Kr, sub);
+        // this thread's events of the chunk
+        uint32_t m[EV];
+        float cf[EV];
+        const bool tok_ok = tok < Lc;
+#pragma unroll
+        for (int j = 0; j < EV; ++j) {
+            const int k = q + j * KL;
+            m[j] = RN_EV_DEAD;
+            cf[j] = 0.f;
+            if (tok_ok && k < KT) {
+                m[j] = e_meta[tok * KT + k];
+                cf[j] = e_coef[tok * KT + k];
             }
-            __syncthreads();
         }
-        if (R > 2) {
-            if (warp == 0) {
-                for (int r = 2; r < R; ++r) {
-                    const int beg = hdr[1 + r], end = hdr[2 + r];
-                    for (int i = beg * G + lane; i < end * G; i += 32) {
-                        const int ev = i / G, sub = i - ev * G;
-                        rn_apply_entry<CS>(e_meta[ev], e_coef[ev], S, xt, yk, Kr, sub);
-                    }
-                    __syncwarp();
+
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int j = 0; j < EV; ++j) {
+                // live event of this round?  (dead events carry bit 24, so the compare fails)
+                if (((m[j] >> 16) & 0x1ffu) != uint32_t(r)) continue;
+                float *row = S + (m[j] & 0xffffu) * CS + sub * 4;
+                float4 s = *reinterpret_cast<float4 *>(row);
+                if (q + j * KL < Kw) {
+                    s.x = fmaf(cf[j], xv.x - s.x, s.x);
+                    s.y = fmaf(cf[j], xv.y - s.y, s.y);
+                    s.z = fmaf(cf[j], xv.z - s.z, s.z);
+                    s.w = fmaf(cf[j], xv.w - s.w, s.w);
+                    *reinterpret_cast<float4 *>(row) = s;
+                } else {
+                    acc.x = fmaf(cf[j], s.x, acc.x);
+                    acc.y = fmaf(cf[j], s.y, acc.y);
+                    acc.z = fmaf(cf[j], s.z, acc.z);
+                    acc.w = fmaf(cf[j], s.w, acc.w);
                 }
             }
             __syncthreads();
         }
 
-        // ---- y[t] = sum_k yk[t][k], fixed order ------------------------------------------------
-        for (int i = tid; i < Lc * G4; i += RN_APPLY_THREADS) {
-            const int t = i / G4, sub = i - t * G4;
-            if (sub * 4 >= cvalid) continue;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float *src = yk + t * Kr * CS + sub * 4;
-#pragma unroll 4
-            for (int k = 0; k < Kr; ++k) {
-                const float4 v = *reinterpret_cast<const float4 *>(src + k * CS);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            rn_store4<T>(y + int64_t(t0 + t) * p.yt + sub * 4, acc);
+        // combine the k-lanes of the token (lanes w = q*G + sub of one warp when TPT <= 32)
+        for (int off = G; off < TPT; off <<= 1) {
+            acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
+            acc.y += __shfl_xor_sync(RN_FULL, acc.y, off);
+            acc.z += __shfl_xor_sync(RN_FULL, acc.z, off);
+            acc.w += __shfl_xor_sync(RN_FULL, acc.w, off);
         }
-        if (more) store_x(xt0 + (buf ^ 1) * (L * CS));
-        __syncthreads();
+        if (q == 0 && tok_ok && chan_ok) rn_store4<T>(y + int64_t(t0 + tok) * p.yt, acc);
     }
 
+    __syncthreads();
     float *dst = p.slot_out + int64_t(bh) * A * C + c0;
-    for (int i = tid; i < A * G4; i += RN_APPLY_THREADS) {
-        const int a = i / G4, sub = i - a * G4;
-        if (sub * 4 < cvalid)
-            *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sub * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sub * 4);
+    for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
+        const int a = i / G, sg = i - a * G;
+        if (sg * 4 < cvalid)
+            *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sg * 4);
     }
 }
 
@@ -538,6 +480,7 @@ struct RnGsuPlan {
     int wide;              // A > 65536: records carry a separate slot array
     int64_t rec_bytes;
     int fast;              // fast apply kernel (C % 4 == 0, narrow records, state in shared memory)
+    int tpt_log2, ev;      // fast kernel: threads per token, events per thread
     int cs, nslices, state_in_smem;
     size_t apply_smem;
     // workspace layout (byte offsets)
@@ -546,9 +489,24 @@ struct RnGsuPlan {
 
 static size_t rn_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-static size_t rn_fast_smem(int64_t A, int cs, int L, int64_t Kr, int NEp) {
+static size_t rn_fast_smem(int64_t A, int cs, int NEp) {
     const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 8, 128);
-    return 2 * rec_stride + (size_t(A) * cs + size_t(L) * Kr * cs + 2 * size_t(L) * cs) * 4;
+    return 2 * rec_stride + size_t(A) * cs * 4;
+}
+
+// fast kernel geometry: 512 threads / next_pow2(L) tokens; events per thread (power of two) or 0 if > 16
+static int rn_fast_geometry(int L, int KT, int cs, int *tpt_log2) {
+    int lp = 1;
+    while (lp < L) lp <<= 1;
+    int tpt = 512 / lp, lg = 0;
+    while ((1 << lg) < tpt) ++lg;
+    *tpt_log2 = lg;
+    const int G = cs / 4;
+    if (tpt > 32 || tpt < G) return 0;
+    const int KL = tpt / G;
+    const int ev = (KT + KL - 1) / KL;
+    if (ev > 16) return 0;
+    return ev <= 1 ? 1 : (ev <= 2 ? 2 : (ev <= 4 ? 4 : (ev <= 8 ? 8 : 16)));
 }
 
 static int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device,
@@ -564,7 +522,7 @@ static int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, in
     pl->NEp = int(rn_align(pl->NE, 4));
     int ept = (pl->NE + RN_GSU_THREADS - 1) / RN_GSU_THREADS;
     pl->ept = ept <= 1 ? 1 : (ept <= 2 ? 2 : (ept <= 4 ? 4 : (ept <= 8 ? 8 : 16)));
-    const size_t ev_bytes = size_t(pl->NE) * 8 + 16;
+    const size_t ev_bytes = size_t(pl->NE) * 8 + 16;  // mass-aware per-event scratch
     pl->smem_tables = (size_t(A) * 8 + ev_bytes) <= RN_SMEM_BUDGET;
     pl->sched_smem = rn_align((pl->smem_tables ? size_t(A) * 8 : 0) + ev_bytes, 16);
     pl->wide = A > 65536;
@@ -576,7 +534,9 @@ static int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, in
     const bool fast_ok = !pl->wide && (C % 4) == 0;
     int best = 0;
     for (int cs = 4; cs <= (fast_ok ? 32 : 128); cs *= 2) {
-        const size_t need = fast_ok ? rn_fast_smem(A, cs, pl->L, Kr, pl->NEp)
+        int lg = 0;
+        if (fast_ok && rn_fast_geometry(pl->L, int(Kw + Kr), cs, &lg) == 0) break;
+        const size_t need = fast_ok ? rn_fast_smem(A, cs, pl->NEp)
                                     : (size_t(A) * cs + size_t(pl->L) * cs + size_t(pl->L) * Kr * cs) * 4;
         if (need > RN_SMEM_BUDGET) break;
         const int64_t ncta = B * H * ((C + cs - 1) / cs);
@@ -587,8 +547,9 @@ static int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, in
         pl->cs = best;
         pl->state_in_smem = 1;
         pl->fast = fast_ok;
-        pl->apply_smem = fast_ok ? rn_fast_smem(A, best, pl->L, Kr, pl->NEp)
+        pl->apply_smem = fast_ok ? rn_fast_smem(A, best, pl->NEp)
                                  : (size_t(A) * best + size_t(pl->L) * best + size_t(pl->L) * Kr * best) * 4;
+        if (fast_ok) pl->ev = rn_fast_geometry(pl->L, int(Kw + Kr), best, &pl->tpt_log2);
     } else {
         // slot state stays in global memory; keep the per-CTA read buffer small
         int cs = 4;
@@ -637,16 +598,18 @@ static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStr
 template <typename T>
 static int rn_launch_apply_fast(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int grid = p.B * p.H * pl.nslices;
-#define RN_CASE(CSV)                                                                                            \
-    if (pl.cs == CSV) {                                                                                         \
-        RN_CUDA(cudaFuncSetAttribute(rn_gsu_apply_fast_kernel<T, CSV>,                                          \
+#define RN_CASE(CSV, EVV)                                                                                       \
+    if (pl.cs == CSV && pl.ev == EVV) {                                                                         \
+        RN_CUDA(cudaFuncSetAttribute(rn_gsu_apply_fast_kernel<T, CSV, EVV>,                                     \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, int(pl.apply_smem)));         \
-        rn_gsu_apply_fast_kernel<T, CSV><<<grid, RN_APPLY_THREADS, pl.apply_smem, stream>>>(p);                 \
+        rn_gsu_apply_fast_kernel<T, CSV, EVV><<<grid, RN_APPLY_THREADS, pl.apply_smem, stream>>>(p, pl.tpt_log2); \
         return 0;                                                                                               \
     }
-    RN_CASE(4) RN_CASE(8) RN_CASE(16) RN_CASE(32)
+#define RN_CASES(CSV) RN_CASE(CSV, 1) RN_CASE(CSV, 2) RN_CASE(CSV, 4) RN_CASE(CSV, 8) RN_CASE(CSV, 16)
+    RN_CASES(4) RN_CASES(8) RN_CASES(16) RN_CASES(32)
+#undef RN_CASES
 #undef RN_CASE
-    rn_set_error("no fast apply kernel for %d channels per CTA", pl.cs);
+    rn_set_error("no fast apply kernel for %d channels per CTA, %d events per thread", pl.cs, pl.ev);
     return 1;
 }
 

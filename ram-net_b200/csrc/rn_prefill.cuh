@@ -16,10 +16,11 @@
 //       reduced over k in a fixed order and y is stored.  Deterministic: no floating-point
 //       atomics anywhere.
 //
-// Chunk record (global workspace, 16-byte aligned, fixed size per call):
-//   u16 header[RN_GSU_HDR]: [0] = R (rounds), [1 + r] = first entry of round r, [1 + R] = entry count
-//   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-21 token in chunk, 22-28 k,
-//                   29 read, 30 zero-contribution read (masked or zero-weight: y += 0)
+// Chunk record (global workspace, 16-byte aligned, fixed size per call); entry e = t * (Kw+Kr) + k
+// keeps the order of the decoded addresses, so the record is written and read coalesced:
+//   u32 header[4]:  [0] = R, the number of rounds of this chunk
+//   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-23 round, 24 dead (no-op event:
+//                   zero weight or masked token)
 //   f32 coef[NEp]:  gain of a write / weight of a read (mass-aware scaling folded in)
 //   u32 slot[NEp]:  only in the wide format (A > 65536)
 #pragma once
@@ -31,18 +32,14 @@ constexpr int RN_GSU_THREADS = 256;               // schedule kernel and generic
 constexpr int RN_GSU_LMAX = 64;                   // longest time chunk
 constexpr int RN_GSU_NE_MAX = 4096;               // most events per chunk (L * (Kw + Kr))
 constexpr int RN_GSU_RMAX = 2 * RN_GSU_LMAX;      // most rounds in a chunk
-constexpr int RN_GSU_HDR = 136;                   // u16 header entries (272 bytes)
-constexpr int RN_GSU_HDR_BYTES = RN_GSU_HDR * 2;
+constexpr int RN_GSU_HDR_BYTES = 16;
 
-constexpr uint32_t RN_EV_READ = 1u << 29;
-constexpr uint32_t RN_EV_ZERO = 1u << 30;
+constexpr uint32_t RN_EV_DEAD = 1u << 24;
 
-__host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int t, int k, bool read, bool zero) {
-    return (slot16 & 0xffffu) | (uint32_t(t) << 16) | (uint32_t(k) << 22) | (read ? RN_EV_READ : 0u) |
-           (zero ? RN_EV_ZERO : 0u);
+__host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int round, bool dead) {
+    return (slot16 & 0xffffu) | (uint32_t(round & 0xff) << 16) | (dead ? RN_EV_DEAD : 0u);
 }
-__host__ __device__ inline int rn_ev_t(uint32_t m) { return int((m >> 16) & 63u); }
-__host__ __device__ inline int rn_ev_k(uint32_t m) { return int((m >> 22) & 127u); }
+__host__ __device__ inline int rn_ev_round(uint32_t m) { return int((m >> 16) & 0xffu); }
 
 struct RnGsuParams {
     // decoded addresses, logical (B,H,Kw+Kr,T)

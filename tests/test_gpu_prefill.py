@@ -121,8 +121,10 @@ def test_inplace_equals_functional_and_chunked_calls_carry_state():
         y, s, m = run_gpu(w[..., lo:hi], r[..., lo:hi], x[:, :, lo:hi], g[..., lo:hi], s, m, mask[:, lo:hi], args["E"],
                           pos[:, lo:hi], K, args["renorm"], False, 1e-6)
         ys.append(y)
-    assert torch.equal(torch.cat(ys, dim=2), full[0])
+    # the state follows the same per-slot operation sequence however the calls are cut: bit-exact;
+    # y sums a token's K reads in an order that depends on the chunk boundaries: rounding only
     assert torch.equal(s, full[1]) and torch.equal(m, full[2])
+    assert_close_stats("y", torch.cat(ys, dim=2), full[0], atol=1e-5, rtol=1e-5, max_err_rate=0.0)
 
 
 def test_all_masked_leaves_state_bit_exact():
