@@ -261,6 +261,15 @@ extern "C" int rn_addr_fwd(const void *w_addr, const void *r_addr, int dtype, co
     RnDeviceGuard guard(device);
     RN_REQUIRE(guard.ok, "cannot make device %d current", device);
 
+    rn_prof_reset();
+    rn_prof_mark(cudaStream_t(stream));
+    if (rn_addr_fwd_fast(w_addr, r_addr, dtype, addr_strides, pos, pos_strides, idx, val, out_strides, B, H, U, P, T, E, A,
+                         Kw, Kr, w_re_norm, r_re_norm, w_neg, r_neg, encode_batch, cudaStream_t(stream)) == 0) {
+        RN_CUDA(cudaGetLastError());
+        rn_prof_mark(cudaStream_t(stream));
+        return 0;
+    }
+
     RnAddrFwdParams p{};
     p.addr[0] = w_addr;
     p.addr[1] = r_addr;

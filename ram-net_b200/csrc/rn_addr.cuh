@@ -225,3 +225,10 @@ __device__ __forceinline__ int rn_pos_mod(int pos, int A) {
     int m = pos % A;
     return m < 0 ? m + A : m;
 }
+
+// Specialised thread-per-row decoder (rn_addr_fast.cu): returns 0 when it launched a kernel for
+// this shape and layout, -1 when the caller should use the general warp-cooperative kernel.
+int rn_addr_fwd_fast(const void *w_addr, const void *r_addr, int dtype, const int64_t *addr_strides, const int32_t *pos,
+                     const int64_t *pos_strides, int32_t *idx, float *val, const int64_t *out_strides, int64_t B,
+                     int64_t H, int64_t U, int64_t P, int64_t T, int64_t E, int64_t A, int64_t Kw, int64_t Kr,
+                     double w_re_norm, double r_re_norm, int w_neg, int r_neg, int encode_batch, cudaStream_t stream);

@@ -137,3 +137,35 @@ def test_errors_are_runtime_errors():
         torch.ops.ramnet_ops.topk_addr_single_forward(addr, 0, 40000, pos, 4, 0.0)
     with pytest.raises(RuntimeError, match="re_norm"):
         torch.ops.ramnet_ops.topk_addr_single_forward(addr[:, :, :, :4], 0, 16, pos, 4, 1.5)
+
+
+@pytest.mark.parametrize("U,P,K,dtype", [(2, 64, 16, torch.bfloat16), (3, 32, 8, torch.bfloat16), (2, 16, 4, torch.float32),
+                                         (2, 64, 16, torch.float16), (3, 32, 8, torch.float32), (2, 64, 16, torch.float32)])
+def test_specialised_and_general_kernels_agree(U, P, K, dtype):
+    """The thread-per-row kernel (contiguous U*P blocks) and the warp-cooperative kernel (any
+    strides) implement the same total order: identical indices, weights equal to rounding.
+    Coarse logits force many exact ties, inside the Top-K and at its boundary."""
+    ops()
+    B, T, H, E = 2, 257, 4, 2
+    g = torch.Generator().manual_seed(11)
+    fine = torch.randn(B, T, H, U, P, generator=g)
+    coarse = torch.randint(-6, 7, (B, T, H, U, P), generator=g).float() * 0.25
+    pos = (torch.arange(T).view(1, T) * 5 + 3).expand(B, T).contiguous()
+    for logits, renorm in ((fine, 0.0), (coarse, 0.5)):
+        logits = logits.to(dtype)
+        logits[0, 3] = float("-inf")                      # inactive token
+        logits[1, 5, :, :, : P - 2] = float("-inf")      # fewer finite addresses than K
+        dense = logits.cuda()
+        padded = torch.zeros(B, T, H, U, P + 8, dtype=dtype, device="cuda")
+        padded[..., :P] = dense
+        strided = padded[..., :P]                          # digit stride P + 8: not the specialised layout
+        a = torch.ops.ramnet_ops.topk_addr_forward(dense.permute(0, 2, 3, 4, 1), dense.flip(1).permute(0, 2, 3, 4, 1),
+                                                   E, P ** U, pos.cuda().int(), K, K, renorm, renorm)
+        b = torch.ops.ramnet_ops.topk_addr_forward(
+            strided.permute(0, 2, 3, 4, 1), torch.flip(padded, dims=[1])[..., :P].permute(0, 2, 3, 4, 1),
+            E, P ** U, pos.cuda().int(), K, K, renorm, renorm)
+        assert torch.equal(a[0], b[0]), f"{int((a[0] != b[0]).sum())} indices differ"
+        assert_close_stats("val", a[1].cpu(), b[1].cpu(), atol=1e-6, rtol=2e-5, max_err_rate=0.0)
+        ref_idx, ref_val = orc.topk_addr(logits.float().permute(0, 2, 3, 4, 1), E, pos, K, renorm)
+        assert torch.equal(a[0][:, :, :K].cpu(), ref_idx)
+        assert_close_stats("val", a[1][:, :, :K].cpu(), ref_val, atol=1e-6, rtol=2e-5, max_err_rate=0.0)
