@@ -141,6 +141,34 @@ int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *idx_strides,
                int64_t Kr, int mass_aware, double eps, int device, void *stream);
 
 /*
+ * Backward of the prefill update / read (non mass-aware reads).
+ * Replaces ramnet_ops::topk_segment_backward
+ * (packages/ramnet-ops/csrc/ram_attn_ops.cpp:267-310, kernels
+ *  packages/ramnet-ops/csrc/ram_attn_segment_parallel.cu:241-606).
+ *
+ *  idx, val, x, gamma, mask, slot_in, mass_in : the forward inputs (same layouts as rn_gsu_fwd).
+ *  d_y          : (B,H,T,C) gradient of y in the dtype of x, strides dy_strides[4];
+ *  d_slot_post, d_mass_post : gradients of the returned state, float32 contiguous.
+ *  d_val        : output (B,H,Kw+Kr,T) through dval_strides[4], ZEROED BY THE CALLER; gradients
+ *                 w.r.t. the positive weight of every event (writes and reads).
+ *  d_x          : output (B,H,T,C) in the dtype of x;  d_gamma: (B,H,T) float32 contiguous;
+ *  d_slot, d_mass : gradients of the initial state, float32 contiguous.
+ *  workspace    : rn_gsu_bwd_workspace_bytes(...) bytes, 256-byte aligned (per write event it holds
+ *                 x - slot_before, C floats, like the reference's replay cache).
+ * Needs C % 4 == 0, A <= 65536 and a channel slice of the state that fits shared memory.
+ */
+int64_t rn_gsu_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
+                                   int device);
+int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *idx_strides, const void *x,
+               const int64_t *x_strides, const void *gamma, const int64_t *gamma_strides, int dtype,
+               const uint8_t *mask, const int64_t *mask_strides, const float *slot_in, const float *mass_in,
+               const void *d_y, const int64_t *dy_strides, const float *d_slot_post, const float *d_mass_post,
+               float *d_val, const int64_t *dval_strides, void *d_x, const int64_t *dx_strides, float *d_gamma,
+               float *d_slot, float *d_mass, void *workspace, int64_t workspace_bytes, int64_t B, int64_t H,
+               int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int mass_aware, double eps, int device,
+               void *stream);
+
+/*
  * Prefill update without any allocation (no counterpart in the reference, which allocates its
  * event buffers with the framework allocator inside the operator).
  *

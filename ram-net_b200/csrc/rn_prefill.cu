@@ -88,13 +88,14 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
 
         // ---- this thread's events ---------------------------------------------------------------
         uint32_t ea[EPT];
-        float ev[EPT], ec[EPT];
+        float ev[EPT], ec[EPT], em[EPT];  // slot, weight, coefficient, mass before the write
         int er[EPT];          // round, or -1 dead (zero weight / masked token), -3 out of range
         uint32_t pend = 0;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             er[j] = -3;
             ec[j] = 0.f;
+            em[j] = 0.f;
             ea[j] = pow2 ? uint32_t(nraw[j] & (A - 1)) : uint32_t(nraw[j] % A);
             ev[j] = fabsf(nval[j]);
             if (ev_t[j] < Lc) {
@@ -117,7 +118,8 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
                 if (!(pend & (1u << j))) continue;
                 if (claim[ea[j]] == uint32_t(j * RN_GSU_THREADS + tid)) {
                     if (ev_k[j] < p.Kw) {
-                        const RnGate g = rn_gate(ev[j], g_cur[ev_t[j]], mass[ea[j]], p.eps);
+                        em[j] = mass[ea[j]];
+                        const RnGate g = rn_gate(ev[j], g_cur[ev_t[j]], em[j], p.eps);
                         mass[ea[j]] = g.mass;
                         ec[j] = g.gain;
                     } else {
@@ -173,6 +175,12 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
             }
         }
         if (tid == 0) *reinterpret_cast<uint32_t *>(rec) = uint32_t(R);
+        if (p.prev_mass != nullptr) {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                if (er[j] >= 0 && ev_k[j] < p.Kw)
+                    p.prev_mass[(int64_t(bh) * p.T + t0 + ev_t[j]) * p.Kw + ev_k[j]] = em[j];
+        }
         __syncthreads();  // gam / tok_live of the next chunk are complete; ev_v / ev_c may be reused
     }
 
@@ -317,7 +325,6 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
 // combined across the group's k-lanes with shuffles in a fixed order: the only shared-memory
 // traffic per event is the slot row itself.  One CTA barrier per round.
 // ------------------------------------------------------------------------------------------
-constexpr int RN_APPLY_THREADS = 512;
 
 template <typename T, int CS, int EV>
 __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2) {
@@ -473,22 +480,6 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
 // ------------------------------------------------------------------------------------------
 constexpr size_t RN_SMEM_BUDGET = 225 * 1024;
 
-struct RnGsuPlan {
-    int L, nchunks, NE, NEp, ept;
-    int smem_tables;       // schedule kernel keeps mass + claim tables in shared memory
-    size_t sched_smem;
-    int wide;              // A > 65536: records carry a separate slot array
-    int64_t rec_bytes;
-    int fast;              // fast apply kernel (C % 4 == 0, narrow records, state in shared memory)
-    int tpt_log2, ev;      // fast kernel: threads per token, events per thread
-    int cs, nslices, state_in_smem;
-    size_t apply_smem;
-    // workspace layout (byte offsets)
-    size_t off_records, off_claim, total;
-};
-
-static size_t rn_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
 static size_t rn_fast_smem(int64_t A, int cs, int NEp) {
     const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 8, 128);
     return 2 * rec_stride + size_t(A) * cs * 4;
@@ -509,7 +500,7 @@ static int rn_fast_geometry(int L, int KT, int cs, int *tpt_log2) {
     return ev <= 1 ? 1 : (ev <= 2 ? 2 : (ev <= 4 ? 4 : (ev <= 8 ? 8 : 16)));
 }
 
-static int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device,
+int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device,
                        RnGsuPlan *pl) {
     RN_REQUIRE(B > 0 && H > 0 && T > 0 && A > 0 && C > 0, "prefill dims must be positive");
     RN_REQUIRE(Kw > 0 && Kw <= 128 && Kr > 0 && Kr <= 128, "Expect 0 < top_k <= 128 (got %lld, %lld)", (long long)Kw,
@@ -611,6 +602,15 @@ static int rn_launch_apply_fast(const RnGsuParams &p, const RnGsuPlan &pl, cudaS
 #undef RN_CASE
     rn_set_error("no fast apply kernel for %d channels per CTA, %d events per thread", pl.cs, pl.ev);
     return 1;
+}
+
+int rn_gsu_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, int dtype, cudaStream_t stream) {
+    if (dtype == RN_F32)
+        return pl.smem_tables ? rn_launch_schedule<float, true>(p, pl, stream) : rn_launch_schedule<float, false>(p, pl, stream);
+    if (dtype == RN_F16)
+        return pl.smem_tables ? rn_launch_schedule<__half, true>(p, pl, stream) : rn_launch_schedule<__half, false>(p, pl, stream);
+    return pl.smem_tables ? rn_launch_schedule<__nv_bfloat16, true>(p, pl, stream)
+                          : rn_launch_schedule<__nv_bfloat16, false>(p, pl, stream);
 }
 
 template <typename T>

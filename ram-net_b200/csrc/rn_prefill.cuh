@@ -69,6 +69,7 @@ struct RnGsuParams {
     int64_t rec_bytes;
     int wide;                 // records carry the separate u32 slot array
     uint32_t *claim;          // global claim table (B*H*A) when the tables do not fit shared memory
+    float *prev_mass;         // optional: mass of the slot before each write, [(bh*T + t)*Kw + k] (backward)
     // apply kernel
     int cs;                   // channels per CTA (multiple of 4)
     int nslices;
@@ -79,6 +80,27 @@ __host__ __device__ inline int rn_gsu_chunk_len(int Kw, int Kr) {
     int L = RN_GSU_NE_MAX / (Kw + Kr);
     return L > RN_GSU_LMAX ? RN_GSU_LMAX : (L < 1 ? 1 : L);
 }
+
+// ---- launch plan shared by the forward and backward entry points ---------------------------------
+constexpr int RN_APPLY_THREADS = 512;
+
+struct RnGsuPlan {
+    int L, nchunks, NE, NEp, ept;
+    int smem_tables;       // schedule kernel keeps mass + claim tables in shared memory
+    size_t sched_smem;
+    int wide;              // A > 65536: records carry a separate slot array
+    int64_t rec_bytes;
+    int fast;              // fast apply kernel (C % 4 == 0, narrow records, state in shared memory)
+    int tpt_log2, ev;      // fast kernel: threads per token, events per thread
+    int cs, nslices, state_in_smem;
+    size_t apply_smem;
+    // workspace layout (byte offsets)
+    size_t off_records, off_claim, total;
+};
+
+int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device, RnGsuPlan *pl);
+int rn_gsu_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, int dtype, cudaStream_t stream);
+inline size_t rn_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---- mbarrier / bulk-copy (TMA 1-D) primitives -----------------------------------------------
 __device__ __forceinline__ uint32_t rn_smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }

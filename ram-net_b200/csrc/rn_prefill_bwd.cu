@@ -1,0 +1,505 @@
+// Prefill backward: gradients of the gated sparse update / read w.r.t. the event weights, x,
+// gamma and the initial state.  Replaces ramnet_ops::topk_segment_backward
+// (packages/ramnet-ops/csrc/ram_attn_ops.cpp:267-310, kernels
+//  packages/ramnet-ops/csrc/ram_attn_segment_parallel.cu:241-416 (replay) and :418-606 (reverse)).
+//
+// Same time-chunk / round structure as the forward pass (rn_prefill.cuh); the chunk records are
+// rebuilt by the schedule kernel (which also stores the mass each write found), then
+//   replay   (one CTA per (b,h,channel slice), chunks forward):  re-runs the state, stores
+//            delta = x - slot_before of every write and accumulates d_r = <slot_at_read, d_y>;
+//   reverse  (same mapping, chunks and rounds backward):  carries d_slot in shared memory;
+//            read:  d_slot[a] += r d_y;   write:  d_gain = <d_slot[a], delta>,
+//            d_x += gain d_slot[a],  d_slot[a] *= 1 - gain;
+//   scalar   (one CTA per (b,h), chunks and rounds backward):  the mass chain: d_w, d_gamma, d_mass.
+// Partial dot products of the channel slices are combined with float atomics (d_r, d_gain).
+#include "rn_prefill.cuh"
+
+struct RnGsuBwdParams {
+    RnGsuParams f;            // forward description (idx/val, x, gamma, mask, records, ...)
+    const void *dy;           // (B,H,T,C) upstream gradient of y, dtype of x
+    int64_t dyb, dyh, dyt;
+    float *delta;             // workspace [(bh*T + t)*Kw + k][C]
+    float *dgain;             // workspace [(bh*T + t)*Kw + k], zeroed by the caller
+    float *dval;              // output (B,H,Kw+Kr,T) via strides, zeroed by the caller
+    int64_t vb, vh, vk, vt;
+    void *dx;                 // output (B,H,T,C), dtype of x
+    int64_t dxb, dxh, dxt;
+    float *dgamma;            // output (B,H,T) contiguous fp32
+    const float *dslot_post;  // (B,H,A,C)
+    float *dslot_out;
+    const float *dmass_post;  // (B,H,A)
+    float *dmass_out;
+    float *dmass_ws;          // global d_mass table when it does not fit shared memory (aliases dmass_out)
+};
+
+__device__ __forceinline__ float rn_group_sum(float v, int G, unsigned mask) {
+    for (int off = 1; off < G; off <<= 1) v += __shfl_xor_sync(mask, v, off);
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------
+// replay / reverse kernels (token-major, see rn_gsu_apply_fast_kernel)
+// ------------------------------------------------------------------------------------------
+template <typename T, int CS, int EV, bool REVERSE>
+__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2) {
+    constexpr int G = CS / 4;
+    const RnGsuParams &p = bp.f;
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ __align__(8) uint64_t mbar[2];
+
+    const int slice = blockIdx.x % p.nslices;
+    const int bh = blockIdx.x / p.nslices;
+    const int b = bh / p.H, h = bh % p.H;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int C = p.C, A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, L = p.L;
+    const int c0 = slice * CS;
+    const int cvalid = min(CS, C - c0);
+    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
+
+    const int TPT = 1 << tpt_log2;
+    const int KL = TPT / G;
+    const int tok = tid >> tpt_log2;
+    const int w = tid & (TPT - 1);
+    const int sub = w % G, q = w / G;
+    const bool chan_ok = sub * 4 < cvalid;
+    const unsigned gmask = (G >= 32 ? 0xffffffffu : ((1u << G) - 1u)) << (lane & ~(G - 1));
+
+    const size_t rec_stride = (size_t(rec_copy) + 127) / 128 * 128;
+    unsigned char *rec0 = dyn;
+    float *S = reinterpret_cast<float *>(dyn + 2 * rec_stride);  // slot slice (replay) or d_slot slice (reverse)
+
+    if (tid == 0) {
+        rn_mbar_init(&mbar[0], 1);
+        rn_mbar_init(&mbar[1], 1);
+        rn_mbar_fence_init();
+    }
+    __syncthreads();
+    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes;
+    const int first = REVERSE ? p.nchunks - 1 : 0;
+    const int step = REVERSE ? -1 : 1;
+    if (tid == 0) {
+        rn_mbar_expect_tx(&mbar[0], rec_copy);
+        rn_bulk_g2s(rec0, records + int64_t(first) * p.rec_bytes, rec_copy, &mbar[0]);
+    }
+    {
+        const float *src = (REVERSE ? bp.dslot_post : p.slot_in) + int64_t(bh) * A * C + c0;
+        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
+            const int a = i / G, sg = i - a * G;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (sg * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sg * 4);
+            *reinterpret_cast<float4 *>(S + a * CS + sg * 4) = v;
+        }
+    }
+    const T *x = static_cast<const T *>(p.x) + b * p.xb + h * p.xh + c0 + sub * 4;
+    const T *dy = static_cast<const T *>(bp.dy) + b * bp.dyb + h * bp.dyh + c0 + sub * 4;
+    T *dx = static_cast<T *>(bp.dx) + b * bp.dxb + h * bp.dxh + c0 + sub * 4;
+
+    auto load_row = [&](const T *base, int64_t tstride, int chunk) {
+        const int t = chunk * L + tok;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (chunk >= 0 && chunk < p.nchunks && tok < L && t < p.T && chan_ok) v = rn_load4<T>(base + int64_t(t) * tstride);
+        return v;
+    };
+    float4 xnext = load_row(x, p.xt, first);
+    float4 dynext = load_row(dy, bp.dyt, first);
+    __syncthreads();
+
+    bool failed = false;
+    for (int it = 0; it < p.nchunks; ++it) {
+        const int chunk = first + it * step;
+        const int buf = it & 1;
+        const int t0 = chunk * L;
+        const int Lc = min(L, p.T - t0);
+        const bool more = it + 1 < p.nchunks;
+        const float4 xv = xnext, dyv = dynext;
+        if (more && tid == 0) {
+            rn_fence_proxy_async();
+            rn_mbar_expect_tx(&mbar[buf ^ 1], rec_copy);
+            rn_bulk_g2s(rec0 + (buf ^ 1) * rec_stride, records + int64_t(chunk + step) * p.rec_bytes, rec_copy,
+                        &mbar[buf ^ 1]);
+        }
+        xnext = load_row(x, p.xt, more ? chunk + step : -1);
+        dynext = load_row(dy, bp.dyt, more ? chunk + step : -1);
+        if (!rn_mbar_wait_bounded(&mbar[buf], (it >> 1) & 1)) failed = true;
+        if (__syncthreads_or(failed)) {
+            if (tid == 0) atomicExch(p.status, 1);
+            if (more) rn_mbar_wait_bounded(&mbar[buf ^ 1], ((it + 1) >> 1) & 1);
+            return;
+        }
+
+        const unsigned char *rec = rec0 + buf * rec_stride;
+        const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
+        const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
+        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
+
+        uint32_t m[EV];
+        float cf[EV];
+        const bool tok_ok = tok < Lc;
+#pragma unroll
+        for (int j = 0; j < EV; ++j) {
+            const int k = q + j * KL;
+            m[j] = RN_EV_DEAD;
+            cf[j] = 0.f;
+            if (tok_ok && k < KT) {
+                m[j] = e_meta[tok * KT + k];
+                cf[j] = e_coef[tok * KT + k];
+            }
+        }
+        // per-write-event rows in the workspaces: index of (t, k) = (bh*T + t)*Kw + k
+        const int64_t wbase = (int64_t(bh) * p.T + t0 + tok) * Kw;
+
+        if (!REVERSE) {
+            for (int r = 0; r < R; ++r) {
+#pragma unroll
+                for (int j = 0; j < EV; ++j) {
+                    if (((m[j] >> 16) & 0x1ffu) != uint32_t(r)) continue;
+                    const int k = q + j * KL;
+                    float *row = S + (m[j] & 0xffffu) * CS + sub * 4;
+                    float4 s = *reinterpret_cast<float4 *>(row);
+                    if (k < Kw) {
+                        const float4 d = make_float4(xv.x - s.x, xv.y - s.y, xv.z - s.z, xv.w - s.w);
+                        if (chan_ok) *reinterpret_cast<float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4) = d;
+                        s.x = fmaf(cf[j], d.x, s.x);
+                        s.y = fmaf(cf[j], d.y, s.y);
+                        s.z = fmaf(cf[j], d.z, s.z);
+                        s.w = fmaf(cf[j], d.w, s.w);
+                        *reinterpret_cast<float4 *>(row) = s;
+                    } else {
+                        float dot = s.x * dyv.x + s.y * dyv.y + s.z * dyv.z + s.w * dyv.w;
+                        dot = rn_group_sum(dot, G, gmask);
+                        if (sub == 0) atomicAdd(bp.dval + b * bp.vb + h * bp.vh + int64_t(k) * bp.vk + int64_t(t0 + tok) * bp.vt, dot);
+                    }
+                }
+                __syncthreads();
+            }
+        } else {
+            // deltas of this thread's write events, fetched before the dependent rounds
+            float4 dl[EV];
+#pragma unroll
+            for (int j = 0; j < EV; ++j) {
+                const int k = q + j * KL;
+                dl[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k < Kw && !(m[j] & RN_EV_DEAD) && chan_ok)
+                    dl[j] = *reinterpret_cast<const float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4);
+            }
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // d_x of this token
+            for (int r = R - 1; r >= 0; --r) {
+#pragma unroll
+                for (int j = 0; j < EV; ++j) {
+                    if (((m[j] >> 16) & 0x1ffu) != uint32_t(r)) continue;
+                    const int k = q + j * KL;
+                    float *row = S + (m[j] & 0xffffu) * CS + sub * 4;
+                    float4 s = *reinterpret_cast<float4 *>(row);
+                    if (k >= Kw) {
+                        s.x = fmaf(cf[j], dyv.x, s.x);
+                        s.y = fmaf(cf[j], dyv.y, s.y);
+                        s.z = fmaf(cf[j], dyv.z, s.z);
+                        s.w = fmaf(cf[j], dyv.w, s.w);
+                    } else {
+                        float dot = s.x * dl[j].x + s.y * dl[j].y + s.z * dl[j].z + s.w * dl[j].w;
+                        dot = rn_group_sum(dot, G, gmask);
+                        if (sub == 0) atomicAdd(bp.dgain + wbase + k, dot);
+                        acc.x = fmaf(cf[j], s.x, acc.x);
+                        acc.y = fmaf(cf[j], s.y, acc.y);
+                        acc.z = fmaf(cf[j], s.z, acc.z);
+                        acc.w = fmaf(cf[j], s.w, acc.w);
+                        const float keep = 1.f - cf[j];
+                        s.x *= keep; s.y *= keep; s.z *= keep; s.w *= keep;
+                    }
+                    *reinterpret_cast<float4 *>(row) = s;
+                }
+                __syncthreads();
+            }
+            for (int off = G; off < TPT; off <<= 1) {
+                acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
+                acc.y += __shfl_xor_sync(RN_FULL, acc.y, off);
+                acc.z += __shfl_xor_sync(RN_FULL, acc.z, off);
+                acc.w += __shfl_xor_sync(RN_FULL, acc.w, off);
+            }
+            if (q == 0 && tok_ok && chan_ok) rn_store4<T>(dx + int64_t(t0 + tok) * bp.dxt, acc);
+        }
+    }
+
+    if (REVERSE) {
+        __syncthreads();
+        float *dst = bp.dslot_out + int64_t(bh) * A * C + c0;
+        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
+            const int a = i / G, sg = i - a * G;
+            if (sg * 4 < cvalid)
+                *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sg * 4);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// scalar reverse kernel: the mass chain
+// ------------------------------------------------------------------------------------------
+struct RnGateBwd {
+    float d_w, d_gamma, d_prev_mass;
+};
+// Adjoint of rn_gate(): given d(loss)/d(gain) and d(loss)/d(new mass).
+__device__ __forceinline__ RnGateBwd rn_gate_bwd(float d_gain, float d_mass, float w, float gamma, float prev_mass, float eps) {
+    const float e = expf(-fabsf(gamma));
+    const float cw = 1.f - w;
+    const float inv_den = 1.f / (gamma >= 0.f ? (w + e * cw) : (cw + e * w));
+    const float alpha = (gamma >= 0.f ? cw * e : cw) * inv_den;
+    const float inv_new = 1.f / (fmaf(alpha, prev_mass, w) + eps);
+    const float d_mass_total = d_mass - d_gain * w * inv_new * inv_new;  // via gain = w / (mass' + eps)
+    const float d_alpha = prev_mass * d_mass_total;
+    RnGateBwd o;
+    o.d_w = inv_new * d_gain + (-e * inv_den * inv_den) * d_alpha + d_mass_total;
+    o.d_gamma = -alpha * (1.f - alpha) * d_alpha;
+    o.d_prev_mass = alpha * d_mass_total;
+    return o;
+}
+
+template <typename T, bool SMEM_TABLE, int EPT>
+__global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const RnGsuBwdParams bp) {
+    const RnGsuParams &p = bp.f;
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ float gam[RN_GSU_LMAX];
+
+    const int bh = blockIdx.x;
+    const int b = bh / p.H, h = bh % p.H;
+    const int tid = threadIdx.x;
+    const int A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, NEp = p.NEp;
+    const bool pow2 = (A & (A - 1)) == 0;
+
+    float *dmass = SMEM_TABLE ? reinterpret_cast<float *>(dyn) : bp.dmass_ws + int64_t(bh) * A;
+    float *dg_term = reinterpret_cast<float *>(dyn + (SMEM_TABLE ? size_t(A) * 4 : 0));  // [L * Kw]
+    const float *src = bp.dmass_post + int64_t(bh) * A;
+    for (int a = tid; a < A; a += RN_GSU_THREADS)
+        if (SMEM_TABLE || src != dmass) dmass[a] = src[a];
+
+    int ev_t[EPT], ev_k[EPT];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+        const int e = j * RN_GSU_THREADS + tid;
+        ev_t[j] = e / KT;
+        ev_k[j] = e - ev_t[j] * KT;
+    }
+    const T *gamma = static_cast<const T *>(p.gamma) + b * p.gb + h * p.gh;
+    const int64_t ibase = b * p.ib + h * p.ih;
+    __syncthreads();
+
+    for (int chunk = p.nchunks - 1; chunk >= 0; --chunk) {
+        const int t0 = chunk * p.L;
+        const int Lc = min(p.L, p.T - t0);
+        const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
+        const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
+        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
+        if (tid < Lc) gam[tid] = rn_to_float<T>(gamma[(t0 + tid) * p.gt]);
+        for (int i = tid; i < Lc * Kw; i += RN_GSU_THREADS) dg_term[i] = 0.f;
+
+        // this thread's write events: round, slot, weight, mass before, d_gain
+        int er[EPT];
+        uint32_t ea[EPT];
+        float ew[EPT], em[EPT], eg[EPT];
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            er[j] = -1;
+            ea[j] = 0;
+            ew[j] = em[j] = eg[j] = 0.f;
+            const int e = j * RN_GSU_THREADS + tid;
+            if (ev_t[j] < Lc && ev_k[j] < Kw && e < NEp) {
+                const uint32_t meta = e_meta[ev_t[j] * KT + ev_k[j]];
+                if (!(meta & RN_EV_DEAD)) {
+                    const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
+                    const int raw = p.idx[o];
+                    er[j] = rn_ev_round(meta);
+                    ea[j] = pow2 ? uint32_t(raw & (A - 1)) : uint32_t(raw % A);
+                    ew[j] = fabsf(p.val[o]);
+                    const int64_t wi = (int64_t(bh) * p.T + t0 + ev_t[j]) * Kw + ev_k[j];
+                    em[j] = p.prev_mass[wi];
+                    eg[j] = bp.dgain[wi];
+                }
+            }
+        }
+        __syncthreads();
+        for (int r = R - 1; r >= 0; --r) {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                if (er[j] != r) continue;
+                const RnGateBwd g = rn_gate_bwd(eg[j], dmass[ea[j]], ew[j], gam[ev_t[j]], em[j], p.eps);
+                dmass[ea[j]] = g.d_prev_mass;
+                dg_term[ev_t[j] * Kw + ev_k[j]] = g.d_gamma;
+                bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt] = g.d_w;
+            }
+            __syncthreads();
+        }
+        if (tid < Lc) {
+            float s = 0.f;
+            for (int k = 0; k < Kw; ++k) s += dg_term[tid * Kw + k];
+            bp.dgamma[(int64_t(bh)) * p.T + t0 + tid] = s;
+        }
+        __syncthreads();
+    }
+    if (SMEM_TABLE) {
+        float *dst = bp.dmass_out + int64_t(bh) * A;
+        for (int a = tid; a < A; a += RN_GSU_THREADS) dst[a] = dmass[a];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+struct RnBwdLayout {
+    size_t off_fwd, off_prev_mass, off_dgain, off_delta, total;
+};
+
+static void rn_bwd_layout(const RnGsuPlan &pl, int64_t B, int64_t H, int64_t T, int64_t C, int64_t Kw, RnBwdLayout *lo) {
+    size_t off = 0;
+    lo->off_fwd = off;
+    off = rn_align(off + pl.total, 256);
+    lo->off_prev_mass = off;
+    off = rn_align(off + size_t(B * H * T * Kw) * 4, 256);
+    lo->off_dgain = off;
+    off = rn_align(off + size_t(B * H * T * Kw) * 4, 256);
+    lo->off_delta = off;
+    off = rn_align(off + size_t(B * H * T * Kw) * size_t(C) * 4, 256);
+    lo->total = off;
+}
+
+extern "C" int64_t rn_gsu_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
+                                              int device) {
+    rn_clear_error();
+    RnGsuPlan pl;
+    if (rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return -1;
+    RnBwdLayout lo;
+    rn_bwd_layout(pl, B, H, T, C, Kw, &lo);
+    return int64_t(lo.total);
+}
+
+template <typename T, bool REVERSE>
+static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaStream_t stream) {
+    const int grid = bp.f.B * bp.f.H * pl.nslices;
+#define RN_CASE(CSV, EVV)                                                                                            \
+    if (pl.cs == CSV && pl.ev == EVV) {                                                                              \
+        RN_CUDA(cudaFuncSetAttribute(rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE>,                                  \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, int(pl.apply_smem)));              \
+        rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE><<<grid, RN_APPLY_THREADS, pl.apply_smem, stream>>>(bp, pl.tpt_log2); \
+        return 0;                                                                                                    \
+    }
+#define RN_CASES(CSV) RN_CASE(CSV, 1) RN_CASE(CSV, 2) RN_CASE(CSV, 4) RN_CASE(CSV, 8) RN_CASE(CSV, 16)
+    RN_CASES(4) RN_CASES(8) RN_CASES(16) RN_CASES(32)
+#undef RN_CASES
+#undef RN_CASE
+    rn_set_error("no backward kernel for %d channels per CTA, %d events per thread", pl.cs, pl.ev);
+    return 1;
+}
+
+template <typename T, bool SMEM>
+static int rn_launch_scalar_bwd(const RnGsuBwdParams &bp, const RnGsuPlan &pl, size_t smem, cudaStream_t stream) {
+    const int bh = bp.f.B * bp.f.H;
+#define RN_CASE(E)                                                                                                   \
+    if (pl.ept == E) {                                                                                               \
+        RN_CUDA(cudaFuncSetAttribute(rn_gsu_scalar_bwd_kernel<T, SMEM, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     int(smem)));                                                                    \
+        rn_gsu_scalar_bwd_kernel<T, SMEM, E><<<bh, RN_GSU_THREADS, smem, stream>>>(bp);                              \
+        return 0;                                                                                                    \
+    }
+    RN_CASE(1) RN_CASE(2) RN_CASE(4) RN_CASE(8) RN_CASE(16)
+#undef RN_CASE
+    rn_set_error("no scalar backward kernel for %d events per thread", pl.ept);
+    return 1;
+}
+
+template <typename T>
+static int rn_run_bwd(const RnGsuBwdParams &bp, const RnGsuPlan &pl, int dtype, cudaStream_t stream) {
+    rn_prof_reset();
+    rn_prof_mark(stream);
+    if (int rc = rn_gsu_launch_schedule(bp.f, pl, dtype, stream)) return rc;
+    RN_CUDA(cudaGetLastError());
+    rn_prof_mark(stream);
+    if (int rc = rn_launch_sweep<T, false>(bp, pl, stream)) return rc;
+    RN_CUDA(cudaGetLastError());
+    rn_prof_mark(stream);
+    if (int rc = rn_launch_sweep<T, true>(bp, pl, stream)) return rc;
+    RN_CUDA(cudaGetLastError());
+    rn_prof_mark(stream);
+    const bool smem_table = size_t(bp.f.A) * 4 + size_t(pl.L) * bp.f.Kw * 4 <= 200 * 1024;
+    const size_t smem = (smem_table ? size_t(bp.f.A) * 4 : 0) + size_t(pl.L) * bp.f.Kw * 4;
+    if (int rc = smem_table ? rn_launch_scalar_bwd<T, true>(bp, pl, smem, stream)
+                            : rn_launch_scalar_bwd<T, false>(bp, pl, smem, stream))
+        return rc;
+    RN_CUDA(cudaGetLastError());
+    rn_prof_mark(stream);
+    return 0;
+}
+
+extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *idx_strides, const void *x,
+                          const int64_t *x_strides, const void *gamma, const int64_t *gamma_strides, int dtype,
+                          const uint8_t *mask, const int64_t *mask_strides, const float *slot_in, const float *mass_in,
+                          const void *d_y, const int64_t *dy_strides, const float *d_slot_post, const float *d_mass_post,
+                          float *d_val, const int64_t *dval_strides, void *d_x, const int64_t *dx_strides, float *d_gamma,
+                          float *d_slot, float *d_mass, void *workspace, int64_t workspace_bytes, int64_t B, int64_t H,
+                          int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int mass_aware, double eps, int device,
+                          void *stream_) {
+    rn_clear_error();
+    RN_REQUIRE(idx && val && idx_strides && x && x_strides && gamma && gamma_strides && slot_in && mass_in && d_y &&
+                   dy_strides && d_slot_post && d_mass_post && d_val && dval_strides && d_x && dx_strides && d_gamma &&
+                   d_slot && d_mass && workspace,
+               "null pointer argument");
+    RN_REQUIRE(dtype == RN_F32 || dtype == RN_F16 || dtype == RN_BF16, "unsupported dtype code %d", dtype);
+    RN_REQUIRE(!mass_aware, "the backward pass of mass_aware reads is not implemented");
+    RN_REQUIRE(x_strides[3] == 1 && dy_strides[3] == 1 && dx_strides[3] == 1, "Tensor x / d_y / d_x last dim must be contiguous");
+    RnGsuPlan pl;
+    if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return rc;
+    RN_REQUIRE(pl.fast, "the backward pass needs C %% 4 == 0, A <= 65536 and a channel slice of the state that fits shared "
+                        "memory (A=%lld, C=%lld)", (long long)A, (long long)C);
+    const size_t esz = dtype == RN_F32 ? 4 : 2;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(d_y) | reinterpret_cast<uintptr_t>(d_x);
+    RN_REQUIRE((ptrs & (4 * esz - 1)) == 0 &&
+                   ((x_strides[0] | x_strides[1] | x_strides[2] | dy_strides[0] | dy_strides[1] | dy_strides[2] |
+                     dx_strides[0] | dx_strides[1] | dx_strides[2]) & 3) == 0,
+               "x, d_y and d_x must be aligned to 4 elements (pointer and strides)");
+    RnBwdLayout lo;
+    rn_bwd_layout(pl, B, H, T, C, Kw, &lo);
+    RN_REQUIRE(workspace_bytes >= int64_t(lo.total), "workspace too small: %lld < %lld bytes", (long long)workspace_bytes,
+               (long long)lo.total);
+    RN_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+    RnDeviceGuard guard(device);
+    RN_REQUIRE(guard.ok, "cannot make device %d current", device);
+    cudaStream_t stream = cudaStream_t(stream_);
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+
+    RnGsuBwdParams bp{};
+    RnGsuParams &p = bp.f;
+    p.idx = idx; p.val = val;
+    p.ib = idx_strides[0]; p.ih = idx_strides[1]; p.ik = idx_strides[2]; p.it = idx_strides[3];
+    p.x = x; p.xb = x_strides[0]; p.xh = x_strides[1]; p.xt = x_strides[2];
+    p.gamma = gamma; p.gb = gamma_strides[0]; p.gh = gamma_strides[1]; p.gt = gamma_strides[2];
+    p.mask = mask;
+    if (mask) { p.mb = mask_strides[0]; p.mt = mask_strides[1]; }
+    p.slot_in = slot_in; p.mass_in = mass_in;
+    p.B = int(B); p.H = int(H); p.T = int(T); p.A = int(A); p.C = int(C); p.Kw = int(Kw); p.Kr = int(Kr);
+    p.L = pl.L; p.nchunks = pl.nchunks; p.NE = pl.NE; p.NEp = pl.NEp;
+    p.mass_aware = 0; p.eps = float(eps);
+    unsigned char *fws = ws + lo.off_fwd;
+    p.status = reinterpret_cast<int *>(fws);
+    p.records = fws + pl.off_records;
+    p.rec_bytes = pl.rec_bytes;
+    p.wide = pl.wide;
+    p.claim = reinterpret_cast<uint32_t *>(fws + pl.off_claim);
+    p.cs = pl.cs; p.nslices = pl.nslices; p.state_in_smem = pl.state_in_smem;
+    p.prev_mass = reinterpret_cast<float *>(ws + lo.off_prev_mass);
+    // the schedule kernel writes the final mass somewhere: d_mass doubles as that scratch before
+    // the scalar kernel overwrites it with the gradient
+    p.mass_out = d_mass;
+
+    bp.dy = d_y; bp.dyb = dy_strides[0]; bp.dyh = dy_strides[1]; bp.dyt = dy_strides[2];
+    bp.delta = reinterpret_cast<float *>(ws + lo.off_delta);
+    bp.dgain = reinterpret_cast<float *>(ws + lo.off_dgain);
+    bp.dval = d_val; bp.vb = dval_strides[0]; bp.vh = dval_strides[1]; bp.vk = dval_strides[2]; bp.vt = dval_strides[3];
+    bp.dx = d_x; bp.dxb = dx_strides[0]; bp.dxh = dx_strides[1]; bp.dxt = dx_strides[2];
+    bp.dgamma = d_gamma;
+    bp.dslot_post = d_slot_post; bp.dslot_out = d_slot;
+    bp.dmass_post = d_mass_post; bp.dmass_out = d_mass; bp.dmass_ws = d_mass;
+
+    RN_REQUIRE(pl.smem_tables, "the backward pass needs the per-head mass table to fit shared memory (A=%lld)", (long long)A);
+    RN_CUDA(cudaMemsetAsync(bp.dgain, 0, size_t(B * H * T * Kw) * 4, stream));
+
+    if (dtype == RN_F32) return rn_run_bwd<float>(bp, pl, dtype, stream);
+    if (dtype == RN_F16) return rn_run_bwd<__half>(bp, pl, dtype, stream);
+    return rn_run_bwd<__nv_bfloat16>(bp, pl, dtype, stream);
+}

@@ -44,6 +44,12 @@ lib.rn_gsu_fwd.restype = ctypes.c_int
 lib.rn_gsu_fwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _i64p, _i32, _ptr, _i64p, _ptr, _ptr, _ptr, _ptr, _ptr,
                            _i64p, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _f64, _i32, _ptr]
 
+lib.rn_gsu_bwd_workspace_bytes.restype = ctypes.c_int64
+lib.rn_gsu_bwd_workspace_bytes.argtypes = [_i64] * 7 + [_i32]
+lib.rn_gsu_bwd.restype = ctypes.c_int
+lib.rn_gsu_bwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _i64p, _i32, _ptr, _i64p, _ptr, _ptr,
+                           _ptr, _i64p, _ptr, _ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _ptr, _ptr, _ptr, _i64,
+                           _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _f64, _i32, _ptr]
 lib.rn_prof_enable.argtypes = [_i32]
 lib.rn_prof_read.argtypes = [ctypes.POINTER(ctypes.c_float), _i32]
 

@@ -42,6 +42,10 @@ _lib.define(
 _lib.define(
     "gsu_forward_(Tensor addr_idx, Tensor addr_val, Tensor x, Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, "
     "Tensor? mask, int w_top_k, int r_top_k, bool mass_aware, float eps) -> Tensor")
+_lib.define(
+    "gsu_backward(Tensor addr_idx, Tensor addr_val, Tensor x, Tensor gamma, Tensor init_slot, Tensor init_mass, "
+    "Tensor? mask, Tensor D_y, Tensor D_post_slot, Tensor D_post_mass, int w_top_k, int r_top_k, bool mass_aware, "
+    "float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)")
 
 
 def _require_cuda(*tensors: torch.Tensor) -> None:
@@ -264,3 +268,44 @@ def _gsu_forward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, w_top
 @torch.library.impl(_lib, "gsu_forward_", "CUDA")
 def _gsu_forward_(addr_idx, addr_val, x, gamma, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps):
     return gsu_forward_impl(addr_idx, addr_val, x, gamma, slot, mass, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps)
+
+
+def _pad_channels(t: torch.Tensor, C4: int) -> torch.Tensor:
+    C = t.shape[-1]
+    return t if C == C4 else torch.nn.functional.pad(t, (0, C4 - C))
+
+
+@torch.library.impl(_lib, "gsu_backward", "CUDA")
+def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y, D_post_slot, D_post_mass, w_top_k,
+                  r_top_k, mass_aware, eps):
+    """(D_val (B,H,Kw+Kr,T) w.r.t. positive weights, D_x in x.dtype, D_gamma fp32, D_slot, D_mass)."""
+    _require_cuda(addr_idx, addr_val, x, gamma, init_slot, init_mass, D_y, D_post_slot, D_post_mass)
+    B, H, T, C = x.shape
+    A = init_slot.shape[2]
+    K = w_top_k + r_top_k
+    C4 = (C + 3) // 4 * 4  # the kernels move channels in groups of four
+    if addr_val.stride() != addr_idx.stride():
+        addr_idx, addr_val = addr_idx.contiguous(), addr_val.contiguous()
+    xs = _pad_channels(x, C4).contiguous()
+    dy = _pad_channels(D_y.to(x.dtype), C4).contiguous()
+    slot_in = _pad_channels(init_slot.to(torch.float32), C4).contiguous()
+    mass_in = init_mass.to(torch.float32).contiguous()
+    d_slot_post = _pad_channels(D_post_slot.to(torch.float32), C4).contiguous()
+    d_mass_post = D_post_mass.to(torch.float32).contiguous()
+    d_val = torch.zeros((B, T, H, K), dtype=torch.float32, device=x.device).permute(0, 2, 3, 1)
+    d_x = torch.empty_like(xs)
+    d_gamma = torch.empty((B, H, T), dtype=torch.float32, device=x.device)
+    d_slot, d_mass = torch.empty_like(slot_in), torch.empty_like(mass_in)
+    if x.numel() == 0:
+        return d_val, d_x[..., :C], d_gamma, d_slot_post[..., :C].clone(), d_mass_post.clone()
+    mask_u8 = None if mask is None else mask.to(torch.bool).view(torch.uint8)
+    nbytes = lib.rn_gsu_bwd_workspace_bytes(B, H, T, A, C4, w_top_k, r_top_k, x.device.index)
+    if nbytes < 0:
+        check(1)
+    ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=x.device)
+    check(lib.rn_gsu_bwd(ptr(addr_idx), ptr(addr_val), strides(addr_idx), ptr(xs), strides(xs), ptr(gamma), strides(gamma),
+                         dtype_code(xs), ptr(mask_u8), None if mask_u8 is None else strides(mask_u8), ptr(slot_in),
+                         ptr(mass_in), ptr(dy), strides(dy), ptr(d_slot_post), ptr(d_mass_post), ptr(d_val), strides(d_val),
+                         ptr(d_x), strides(d_x), ptr(d_gamma), ptr(d_slot), ptr(d_mass), ptr(ws), int(nbytes), B, H, T, A,
+                         C4, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    return d_val, d_x[..., :C], d_gamma, d_slot[..., :C], d_mass

@@ -115,3 +115,43 @@ def _(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, w_top_k, r_top_k
 @torch.library.register_fake("ramnet_ops::gsu_forward_")
 def _(addr_idx, addr_val, x, gamma, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps):
     return _y_like(x)
+
+
+@torch.library.register_fake("ramnet_ops::gsu_backward")
+def _(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y, D_post_slot, D_post_mass, w_top_k, r_top_k,
+      mass_aware, eps):
+    B, H, T, C = x.shape
+    return (_token_major(x, B, H, w_top_k + r_top_k, T, torch.float32), x.new_empty(x.shape),
+            x.new_empty((B, H, T), dtype=torch.float32), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
+            init_mass.new_empty(init_mass.shape, dtype=torch.float32))
+
+
+def _gsu_setup(ctx, inputs, output):
+    addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, w_top_k, r_top_k, mass_aware, eps = inputs
+    ctx.opts = (w_top_k, r_top_k, mass_aware, eps, mask is not None)
+    saved = [addr_idx, addr_val, x, gamma, init_slot, init_mass] + ([mask] if mask is not None else [])
+    ctx.save_for_backward(*saved)
+    ctx.set_materialize_grads(False)
+
+
+def _gsu_backward(ctx, D_y, D_slot, D_mass):
+    w_top_k, r_top_k, mass_aware, eps, has_mask = ctx.opts
+    addr_idx, addr_val, x, gamma, slot, mass = ctx.saved_tensors[:6]
+    mask = ctx.saved_tensors[6] if has_mask else None
+    if D_y is None and D_slot is None and D_mass is None:
+        return (None,) * 11
+    d_val, d_x, d_gamma, d_slot, d_mass = torch.ops.ramnet_ops.gsu_backward(
+        addr_idx, addr_val, x, gamma, slot, mass, mask,
+        torch.zeros_like(x) if D_y is None else D_y,
+        torch.zeros_like(slot, dtype=torch.float32) if D_slot is None else D_slot,
+        torch.zeros_like(mass, dtype=torch.float32) if D_mass is None else D_mass,
+        w_top_k, r_top_k, mass_aware, eps)
+    need = ctx.needs_input_grad
+    # d_val is w.r.t. the positive weight of each event; the joined decode stored reads negated and its
+    # backward expects exactly this convention
+    return (None, d_val if need[1] else None, d_x.to(x.dtype) if need[2] else None,
+            d_gamma.to(gamma.dtype) if need[3] else None, d_slot.to(slot.dtype) if need[4] else None,
+            d_mass.to(mass.dtype) if need[5] else None, None, None, None, None, None)
+
+
+torch.library.register_autograd("ramnet_ops::gsu_forward", _gsu_backward, setup_context=_gsu_setup)

@@ -1,0 +1,101 @@
+"""GPU parity of the backward pass (address backward + prefill backward) through the public API,
+against the reference's fp64 gradients (golden fixtures) and the CPU oracle's autograd."""
+import pytest
+import torch
+
+from oracle import ramnet_oracle as orc
+from tests.gpu_common import ops, randn
+from tests.helpers import FP32_TOL, assert_close_stats, load, t
+
+pytestmark = pytest.mark.gpu
+
+GRAD_TOL_BF16 = dict(atol=7.5e-2, rtol=7.5e-2, max_err_rate=0.02, max_q99=2.0)
+
+
+def run_api(w, r, x, g, slot, mass, mask, pos, E, K, renorm, eps, d_y, d_slot, d_mass, dtype):
+    """Public API on GPU with autograd; inputs in (B,T,H,...) layout on CPU."""
+    import ramnet_ops
+    leaves = [v.to(dtype).cuda().requires_grad_(True) for v in (w, r, x, g)] + \
+             [v.float().cuda().requires_grad_(True) for v in (slot, mass)]
+    y, (s1, m1) = ramnet_ops.random_access_memory_attention(
+        leaves[0], leaves[1], leaves[2], leaves[3], (leaves[4], leaves[5]),
+        mask=None if mask is None else mask.cuda(), embed_num=E, position_ids=pos.cuda(), top_k=K, top_k_re_norm=renorm,
+        eps=eps, impl_backend="cuda")
+    up = d_y.to(dtype).cuda()
+    if mask is not None:
+        up = up * mask.cuda()[:, :, None, None]
+    grads = torch.autograd.grad((y, s1, m1), leaves, (up, d_slot.cuda(), d_mass.cuda()))
+    return (y, s1, m1), [gr.float().cpu() for gr in grads]
+
+
+def valid(gr, mask):
+    return gr if mask is None else gr[mask]
+
+
+@pytest.mark.parametrize("name", ["ram_grads_masked.npz", "ram_grads_plain.npz"])
+def test_gradients_match_reference_golden(name):
+    ops()
+    z = load(name)
+    B, H, U, P, T, Kw, Kr, C, E, ma = (int(v) for v in z["meta"])
+    mask = t(z["mask"]) if z["mask"].size else None
+    rn = tuple(float(v) for v in z["renorm"])
+    _, grads = run_api(t(z["w_addr"]), t(z["r_addr"]), t(z["values"]), t(z["gamma"]), t(z["init_slot"]), t(z["init_mass"]),
+                       mask, t(z["pos"]), E, (Kw, Kr), rn, float(z["eps"]), t(z["d_y"]), t(z["d_slot"]), t(z["d_mass"]),
+                       torch.float32)
+    names = ("D_w", "D_r", "D_x", "D_gamma", "D_slot", "D_mass")
+    for n, got in zip(names, grads):
+        ref = t(z["out64_" + n])
+        if n in ("D_w", "D_r", "D_x", "D_gamma"):
+            got, ref = valid(got, mask), valid(ref, mask)
+        assert_close_stats(n, got, ref, **FP32_TOL)
+
+
+@pytest.mark.parametrize("B,H,U,P,T,C,K,dtype,masked", [
+    (2, 4, 2, 16, 130, 32, (4, 4), torch.float32, False),
+    (1, 2, 2, 64, 96, 128, (16, 16), torch.bfloat16, False),
+    (2, 2, 3, 4, 70, 29, (8, 3), torch.float32, True),       # C not a multiple of 4: padded internally
+    (1, 2, 2, 2, 90, 8, (2, 3), torch.float32, False),       # 4 slots: long chains inside a chunk
+    (1, 2, 4, 4, 40, 16, (40, 24), torch.float32, True),
+])
+def test_gradients_match_oracle_autograd(B, H, U, P, T, C, K, dtype, masked):
+    ops()
+    A = P ** U
+    w = randn((B, T, H, U, P), 1, dtype)
+    r = randn((B, T, H, U, P), 2, dtype)
+    x = randn((B, T, H, C), 3, dtype)
+    g = (0.5 * randn((B, T, H), 4)).to(dtype)
+    slot = randn((B, H, A, C), 5)
+    mass = torch.rand(B, H, A, generator=torch.Generator().manual_seed(6)) + 0.1
+    d_y, d_slot, d_mass = randn((B, T, H, C), 7), randn((B, H, A, C), 8), randn((B, H, A), 9)
+    if masked:
+        mask = torch.ones(B, T, dtype=torch.bool)
+        mask[:, :5] = False
+        mask[0, T // 2: T // 2 + 7] = False
+        pos = ((mask.long().cumsum(-1) - 1) * 3 + 11).masked_fill(~mask, 0)
+    else:
+        mask, pos = None, torch.arange(T).view(1, T).expand(B, T).contiguous()
+    E, renorm, eps = H // 2, (0.25, 0.75), 1e-6
+    _, grads = run_api(w, r, x, g, slot, mass, mask, pos, E, K, renorm, eps, d_y, d_slot, d_mass, dtype)
+    up = d_y.to(dtype).float()
+    if mask is not None:
+        up = up * mask[:, :, None, None]
+    _, ref = orc.ram_attn_grads(
+        w.float().permute(0, 2, 3, 4, 1), r.float().permute(0, 2, 3, 4, 1), x.float().permute(0, 2, 1, 3),
+        g.float().permute(0, 2, 1), slot, mass, mask, E, pos, K, renorm, False, eps, up.permute(0, 2, 1, 3), d_slot, d_mass)
+    ref = [ref[0].permute(0, 4, 1, 2, 3), ref[1].permute(0, 4, 1, 2, 3), ref[2].permute(0, 2, 1, 3), ref[3].permute(0, 2, 1),
+           ref[4], ref[5]]
+    tol = FP32_TOL if dtype == torch.float32 else GRAD_TOL_BF16
+    for n, got, want in zip(("D_w", "D_r", "D_x", "D_gamma", "D_slot", "D_mass"), grads, ref):
+        if n in ("D_w", "D_r", "D_x", "D_gamma"):
+            got, want = valid(got, mask), valid(want, mask)
+        assert_close_stats(n, got, want, **(FP32_TOL if n in ("D_slot", "D_mass") and dtype == torch.float32 else tol))
+
+
+def test_mass_aware_backward_is_refused_loudly():
+    ops()
+    import ramnet_ops
+    w = torch.randn(1, 8, 2, 2, 4, device="cuda", requires_grad=True)
+    y, _ = ramnet_ops.random_access_memory_attention(w, w.detach(), torch.randn(1, 8, 2, 4, device="cuda"), top_k=2,
+                                                     mass_aware=True, impl_backend="cuda")
+    with pytest.raises(RuntimeError, match="mass_aware"):
+        y.sum().backward()
