@@ -221,6 +221,35 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
 
+    del host, y_host
+    # backward of the same step (address backward + update/read backward), timed per kernel
+    bwd = None
+    if not args.no_extra:
+        idx, val = ops.topk_addr_forward(w_view, r_view, E, A, pos, K, K, 0.0, 0.0)
+        d_y = torch.randn(B, T, H, C, device=device, dtype=torch.bfloat16).permute(0, 2, 1, 3)
+        d_slot = torch.zeros_like(slot0)
+        d_mass = torch.zeros_like(mass0)
+        shape6 = [B, H, U, P, A, T]
+        tb = {"schedule": [], "replay": [], "reverse": [], "scalar": [], "addr_bwd": []}
+        lib().rn_prof_enable(1)
+        for i in range(3):
+            d_val, d_x, d_g, d_s, d_m = ops.gsu_backward(idx, val, x_view, g_view, slot0, mass0, None, d_y, d_slot, d_mass,
+                                                         K, K, False, 1e-12)
+            ts = kernel_times(6)
+            dw, dr = ops.topk_addr_backward(idx, val, w_view, r_view, d_val, E, pos, K, K, 0.0, 0.0, shape6, torch.bfloat16)
+            ta = kernel_times(2)
+            if i > 0:
+                for n, v in zip(("schedule", "replay", "reverse", "scalar"), ts):
+                    tb[n].append(v)
+                tb["addr_bwd"] += ta
+        lib().rn_prof_enable(0)
+        torch.cuda.synchronize()
+        bwd = {n: sum(v) / max(len(v), 1) for n, v in tb.items()}
+        bwd["total_ms"] = sum(bwd.values())
+        del d_val, d_x, d_g, d_s, d_m, dw, dr, d_y, d_slot, d_mass, idx, val
+        torch.cuda.empty_cache()
+
+
     def mean(v):
         return sum(v) / max(len(v), 1)
 
@@ -229,9 +258,9 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
     return dict(
         tokens_per_step=B * T, ms_total=ms, steps=args.steps, e2e_ms_total=e2e_ms, e2e_steps=e2e_steps,
         h2d=h2d, d2h=d2h, launches_per_step=3, clocks=clocks.summary(),
-        kernels={"rn_addr_fwd_kernel": mean(t_addr), "rn_gsu_schedule_kernel": mean(t_sched),
-                 "rn_gsu_apply_kernel": mean(t_apply)},
-        dominant=("rn_gsu_apply_kernel", B * H * per_bh, mean(t_apply)), step_bytes=step_bytes,
+        kernels={"rn_addr_fast_kernel": mean(t_addr), "rn_gsu_schedule_kernel": mean(t_sched),
+                 "rn_gsu_apply_fast_kernel": mean(t_apply)},
+        dominant=("rn_gsu_apply_fast_kernel", B * H * per_bh, mean(t_apply)), step_bytes=step_bytes, bwd=bwd,
         workload="prefill_fwd B8 T16384 H16 U2 P64(A4096) Kw16 Kr16 C128 bf16, CAPE on 8 heads, zero fp32 state")
 
 
@@ -426,6 +455,12 @@ def main():
                           "frac": m["step_bytes"] / (ms_per_step / 1e3) / 1e9 / peak},
         "kernel_ms": m["kernels"],
     }
+    if m.get("bwd"):
+        bw = m["bwd"]
+        bwd_bytes = SHAPES["prefill"]["B"] * SHAPES["prefill"]["H"] * 35.7e6
+        line["prefill_bwd"] = {"kernel_ms": bw, "fwd_plus_bwd_tokens_per_s": world * m["tokens_per_step"] /
+                               ((ms_per_step + bw["total_ms"]) / 1e3),
+                               "algorithmic_bytes": bwd_bytes, "frac": bwd_bytes / (bw["total_ms"] / 1e3) / 1e9 / peak}
     if extra:
         d, a = extra["decode"], extra["addr"]
         line["decode"] = {"tokens_per_s": world * d["tokens_per_s"], "ms_per_step": d["ms_per_step"], "kernel_ms": d["kernel_ms"],
