@@ -1,237 +1,10 @@
-// Thread-per-row address decoder for the shapes the models use ((U,P,K) known at compile time).
-//
-// One thread decodes one (batch, token, head, write|read) block of U*P logits entirely in
-// registers with fully unrolled compare-exchange networks, so no shuffles and no shared memory
-// are needed and a warp's 32 rows progress in lockstep without divergence:
-//   per digit   Top-K of the P logits: sort blocks of K (Batcher odd-even merge sort), then fold
-//               the blocks pairwise with a bitonic top-half + bitonic merge.  16-bit inputs use one
-//               32-bit key per logit, (ordered bits << 16) | (0xffff - p), so a compare-exchange
-//               is an integer max/min pair.
-//   per level   candidates (i, j) with (i+1)(j+1) <= K between the sorted prefixes and the sorted
-//               digit; row 0 and column 0 of that table are already sorted, only the remainder is
-//               sorted, then the blocks are folded the same way.  Keys are (ordered fp32 score,
-//               ~index) pairs compared as 64-bit integers.
-// Same total order, same fp32 left-fold score and same special cases as rn_addr.cuh; the
-// general warp-cooperative kernel remains the path for every other (U,P,K).
-#include "rn_addr.cuh"
-
-#include <type_traits>
+// Address kernel built on the thread-per-row decoder (rn_addr_fast.cuh): one thread per
+// (batch, token, head, write|read) row, 16-byte vector loads of the contiguous U*P block and
+// 16-byte vector stores of the K indices / weights.
+#include "rn_addr_fast.cuh"
 
 namespace {
-
-__device__ __forceinline__ float fast_ex2(float x) {
-    float y;
-    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float fast_lg2(float x) {
-    float y;
-    asm("lg2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// ---- keys ------------------------------------------------------------------------------------
-struct Key32 {
-    uint32_t v;
-};
-struct Key64 {
-    uint32_t hi, lo;
-};
-__device__ __forceinline__ bool key_less(const Key32 &a, const Key32 &b) { return a.v < b.v; }
-__device__ __forceinline__ bool key_less(const Key64 &a, const Key64 &b) {
-    return a.hi < b.hi || (a.hi == b.hi && a.lo < b.lo);
-}
-__device__ __forceinline__ void cmpx(Key32 &a, Key32 &b) {  // afterwards a >= b
-    const uint32_t mx = max(a.v, b.v), mn = min(a.v, b.v);
-    a.v = mx;
-    b.v = mn;
-}
-__device__ __forceinline__ void cmpx(Key64 &a, Key64 &b) {
-    if (key_less(a, b)) {
-        const Key64 t = a;
-        a = b;
-        b = t;
-    }
-}
-__device__ __forceinline__ Key32 key_max(const Key32 &a, const Key32 &b) { return Key32{max(a.v, b.v)}; }
-__device__ __forceinline__ Key64 key_max(const Key64 &a, const Key64 &b) { return key_less(a, b) ? b : a; }
-__device__ __forceinline__ Key32 key_lowest(Key32) { return Key32{0u}; }
-__device__ __forceinline__ Key64 key_lowest(Key64) { return Key64{0u, 0u}; }
-
-// ---- networks: every index is a template constant, so key arrays stay in registers ------------
-// Batcher's odd-even merge sort (descending), recursive formulation.
-template <int I, int End, int Step, int R, typename Key>
-__device__ __forceinline__ void oem_cmp_row(Key *k) {
-    if constexpr (I + R < End) {
-        cmpx(k[I], k[I + R]);
-        oem_cmp_row<I + Step, End, Step, R>(k);
-    }
-}
-template <int Lo, int N, int R, typename Key>
-__device__ __forceinline__ void oem_merge(Key *k) {
-    constexpr int M = R * 2;
-    if constexpr (M < N) {
-        oem_merge<Lo, N, M>(k);
-        oem_merge<Lo + R, N, M>(k);
-        oem_cmp_row<Lo + R, Lo + N, M, R>(k);
-    } else {
-        cmpx(k[Lo], k[Lo + R]);
-    }
-}
-template <int Lo, int N, typename Key>
-__device__ __forceinline__ void oem_sort_range(Key *k) {
-    if constexpr (N > 1) {
-        oem_sort_range<Lo, N / 2>(k);
-        oem_sort_range<Lo + N / 2, N / 2>(k);
-        oem_merge<Lo, N, 1>(k);
-    }
-}
-template <int N, typename Key>
-__device__ __forceinline__ void oem_sort_desc(Key *k) {
-    oem_sort_range<0, N>(k);
-}
-// k[0..N) bitonic -> sorted descending
-template <int I, int N, int S, typename Key>
-__device__ __forceinline__ void bitonic_row(Key *k) {
-    if constexpr (I < N) {
-        if constexpr ((I & S) == 0) cmpx(k[I], k[I | S]);
-        bitonic_row<I + 1, N, S>(k);
-    }
-}
-template <int N, int S, typename Key>
-__device__ __forceinline__ void bitonic_stage(Key *k) {
-    if constexpr (S >= 1) {
-        bitonic_row<0, N, S>(k);
-        bitonic_stage<N, S / 2>(k);
-    }
-}
-template <int N, typename Key>
-__device__ __forceinline__ void bitonic_merge_desc(Key *k) {
-    bitonic_stage<N, N / 2>(k);
-}
-// a[0..K) and b[0..K) sorted descending -> a = the K largest of both, sorted descending
-template <int K, typename Key>
-__device__ __forceinline__ void fold_topk(Key *a, const Key *b) {
-#pragma unroll
-    for (int i = 0; i < K; ++i) a[i] = key_max(a[i], b[K - 1 - i]);
-    bitonic_merge_desc<K>(a);
-}
-
-// candidates (i, j) with i >= 1, j >= 1 and (i+1)(j+1) <= K, in row-major order
-__host__ __device__ constexpr int rn_remainder_before(int K, int i) {
-    int n = 0;
-    for (int ii = 1; ii < i; ++ii) n += (K / (ii + 1) > 1) ? K / (ii + 1) - 1 : 0;
-    return n;
-}
-__host__ __device__ constexpr int rn_remainder_count(int K) { return rn_remainder_before(K, K); }
-
-template <int Lo, int Hi, typename F>
-__device__ __forceinline__ void static_for(F &&f) {
-    if constexpr (Lo < Hi) {
-        f(std::integral_constant<int, Lo>{});
-        static_for<Lo + 1, Hi>(f);
-    }
-}
-
-// Writes candidate (I, J), (I+1)(J+1) <= K, I, J >= 1, into its slot of remainder block BID and
-// recurses over the rest of the table; every index is a template constant.
-template <int K, int BID, int I, int J>
-struct RemFill {
-    static __device__ __forceinline__ void run(Key64 (&blk)[K], const float (&beam_s)[K], const int (&beam_i)[K],
-                                               const float (&dv)[K], const int (&dp)[K]) {
-        if constexpr ((I + 1) * (J + 1) <= K) {
-            constexpr int pos = rn_remainder_before(K, I) + (J - 1);
-            if constexpr (pos / K == BID)
-                blk[pos % K] = Key64{rn_ord(beam_s[I] + dv[J] + 0.0f), ~uint32_t(beam_i[I] + dp[J])};
-            if constexpr (J + 1 < K) RemFill<K, BID, I, J + 1>::run(blk, beam_s, beam_i, dv, dp);
-            else if constexpr (I + 1 < K) RemFill<K, BID, I + 1, 1>::run(blk, beam_s, beam_i, dv, dp);
-        } else if constexpr (I + 1 < K && J > 1) {
-            RemFill<K, BID, I + 1, 1>::run(blk, beam_s, beam_i, dv, dp);  // rest of row I is out of range too
-        }
-    }
-};
-
-template <typename T> struct Raw;  // logits as stored
-template <> struct Raw<float> {
-    static constexpr bool wide = true;
-};
-template <> struct Raw<__half> {
-    static constexpr bool wide = false;
-};
-template <> struct Raw<__nv_bfloat16> {
-    static constexpr bool wide = false;
-};
-
-__device__ __forceinline__ uint32_t ord16_from_bf16(uint32_t h) {
-    if (h == 0x8000u) h = 0u;  // -0.0 ties with +0.0
-    return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
-}
-__device__ __forceinline__ float f32_from_ord16_bf16(uint32_t o) {
-    const uint32_t h = (o & 0x8000u) ? (o & 0x7fffu) : (~o & 0xffffu);
-    return __uint_as_float(h << 16);
-}
-__device__ __forceinline__ float f32_from_ord16_half(uint32_t o) {
-    const uint32_t h = (o & 0x8000u) ? (o & 0x7fffu) : (~o & 0xffffu);
-    return __half2float(__ushort_as_half((unsigned short)h));
-}
-
-template <typename T>
-__device__ __forceinline__ float digit_value(const Key32 &k) {
-    if constexpr (std::is_same<T, __nv_bfloat16>::value) return f32_from_ord16_bf16(k.v >> 16);
-    else return f32_from_ord16_half(k.v >> 16);
-}
-__device__ __forceinline__ int digit_index(const Key32 &k) { return int(0xffffu - (k.v & 0xffffu)); }
-template <typename T>
-__device__ __forceinline__ float digit_value(const Key64 &k) { return rn_unord(k.hi); }
-__device__ __forceinline__ int digit_index(const Key64 &k) { return int(~k.lo); }
-
-// Visit the P logits of one digit as floats; q is a compile-time index after unrolling.
-template <typename T, int P, typename F>
-__device__ __forceinline__ void rn_for_each_logit(const T *src, F &&f) {
-    if constexpr (Raw<T>::wide) {
-#pragma unroll
-        for (int v = 0; v < P / 4; ++v) {
-            const float4 x = reinterpret_cast<const float4 *>(src)[v];
-            f(4 * v, x.x); f(4 * v + 1, x.y); f(4 * v + 2, x.z); f(4 * v + 3, x.w);
-        }
-    } else {
-#pragma unroll
-        for (int v = 0; v < P / 8; ++v) {
-            const uint4 raw = reinterpret_cast<const uint4 *>(src)[v];
-            const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t lo = wds[c] & 0xffffu, hi = wds[c] >> 16;
-                if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-                    f(8 * v + 2 * c, __uint_as_float(lo << 16));
-                    f(8 * v + 2 * c + 1, __uint_as_float(hi << 16));
-                } else {
-                    f(8 * v + 2 * c, __half2float(__ushort_as_half((unsigned short)lo)));
-                    f(8 * v + 2 * c + 1, __half2float(__ushort_as_half((unsigned short)hi)));
-                }
-            }
-        }
-    }
-}
-
-template <typename T, int P>
-__device__ __forceinline__ void rn_make_keys(const T *src, Key64 *dk) {
-    rn_for_each_logit<T, P>(src, [&](int q, float x) { dk[q] = Key64{rn_ord(x + 0.0f), ~uint32_t(q)}; });
-}
-template <typename T, int P>
-__device__ __forceinline__ void rn_make_keys(const T *src, Key32 *dk) {
-#pragma unroll
-    for (int v = 0; v < P / 8; ++v) {
-        const uint4 raw = reinterpret_cast<const uint4 *>(src)[v];
-        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int q = 8 * v + 2 * c;
-            dk[q] = Key32{(ord16_from_bf16(wds[c] & 0xffffu) << 16) | (0xffffu - uint32_t(q))};
-            dk[q + 1] = Key32{(ord16_from_bf16(wds[c] >> 16) << 16) | (0xffffu - uint32_t(q + 1))};
-        }
-    }
-}
+using namespace rn_fast;
 
 struct FastParams {
     const void *addr[2];
@@ -253,12 +26,6 @@ constexpr int FAST_THREADS = 128;
 
 template <typename T, int U, int P, int K>
 __global__ void __launch_bounds__(FAST_THREADS) rn_addr_fast_kernel(const FastParams p) {
-    using DKey = typename std::conditional<Raw<T>::wide, Key64, Key32>::type;
-    constexpr int NB = P / K;                 // digit blocks of K logits
-    constexpr float LOG2E = 1.4426950408889634f;
-    constexpr float LN2 = 0.6931471805599453f;
-    static_assert(P % K == 0 && (K & (K - 1)) == 0 && K >= 2, "P must be a multiple of the power-of-two K");
-
     // rows of one tensor are adjacent across the CTA: item = which * n_rows + row
     const int64_t item = int64_t(blockIdx.x) * FAST_THREADS + threadIdx.x;
     if (item >= p.n_rows * p.nwhich) return;
@@ -269,90 +36,9 @@ __global__ void __launch_bounds__(FAST_THREADS) rn_addr_fast_kernel(const FastPa
     const int b = int(row / (int64_t(p.H) * p.T));
     const T *src = static_cast<const T *>(p.addr[which]) + b * p.sb + h * p.sh + t * p.st;
 
-    float beam_s[K];
-    int beam_i[K];
-    float lse_total = 0.f;
-    bool inactive = false;
-    int stride = 1;
-
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-        // ---- digit u: keys, log-sum-exp, sorted Top-K -------------------------------------------
-        // three passes over the row's P logits (L1-resident after the first): max, sum of
-        // exponentials, keys; nothing but the keys stays in registers
-        DKey dk[P];
-        float xmax = -INFINITY;
-        rn_for_each_logit<T, P>(src + u * P, [&](int, float x) { xmax = fmaxf(xmax, x); });
-        if (xmax == -INFINITY) {
-            inactive = true;
-        } else {
-            float s = 0.f;
-            const float off = xmax * LOG2E;
-            rn_for_each_logit<T, P>(src + u * P, [&](int, float x) { s += fast_ex2(fmaf(x, LOG2E, -off)); });
-            lse_total += xmax + fast_lg2(s) * LN2;
-        }
-        rn_make_keys<T, P>(src + u * P, dk);
-        static_for<0, NB>([&](auto BI) __attribute__((always_inline)) { oem_sort_desc<K>(dk + decltype(BI)::value * K); });
-        static_for<1, NB>([&](auto BI) __attribute__((always_inline)) { fold_topk<K>(dk, dk + decltype(BI)::value * K); });
-        // dk[0..K) = this digit's K best logits, sorted descending
-
-        if (u == 0) {
-#pragma unroll
-            for (int e = 0; e < K; ++e) {
-                beam_s[e] = digit_value<T>(dk[e]) + 0.0f;
-                beam_i[e] = digit_index(dk[e]);
-            }
-        } else {
-            // ---- candidates (i, j), (i+1)(j+1) <= K --------------------------------------------
-            float dv[K];
-            int dp[K];
-#pragma unroll
-            for (int e = 0; e < K; ++e) {
-                dv[e] = digit_value<T>(dk[e]);
-                dp[e] = digit_index(dk[e]) * stride;
-            }
-            // block 0: row i = 0 (sorted);  block 1: column j = 0, i >= 1 (sorted) + one pad
-            Key64 best[K], blk[K];
-#pragma unroll
-            for (int j = 0; j < K; ++j) best[j] = Key64{rn_ord(beam_s[0] + dv[j] + 0.0f), ~uint32_t(beam_i[0] + dp[j])};
-#pragma unroll
-            for (int i = 1; i < K; ++i) blk[i - 1] = Key64{rn_ord(beam_s[i] + dv[0] + 0.0f), ~uint32_t(beam_i[i] + dp[0])};
-            blk[K - 1] = Key64{0u, 0u};
-            fold_topk<K>(best, blk);
-            // the remainder (i >= 1, j >= 1), K at a time, each block sorted then folded in.
-            // Position of (i, j) in the remainder list: rows before it + (j - 1); all of it folds
-            // to constants once the loops are unrolled.
-            constexpr int NREM = rn_remainder_count(K);
-            constexpr int NBLK = (NREM + K - 1) / K;
-            static_for<0, NBLK>([&](auto BID) __attribute__((always_inline)) {
-#pragma unroll
-                for (int e = 0; e < K; ++e) blk[e] = Key64{0u, 0u};
-                RemFill<K, decltype(BID)::value, 1, 1>::run(blk, beam_s, beam_i, dv, dp);
-                oem_sort_desc<K>(blk);
-                fold_topk<K>(best, blk);
-            });
-#pragma unroll
-            for (int e = 0; e < K; ++e) {
-                beam_s[e] = rn_unord(best[e].hi);
-                beam_i[e] = int(~best[e].lo);
-            }
-        }
-        stride *= P;
-    }
-
-    // ---- weights and stores --------------------------------------------------------------------
-    float logq[K];
-#pragma unroll
-    for (int e = 0; e < K; ++e) logq[e] = beam_s[e] - lse_total;
-    const float rho = p.re_norm[which];
-    if (rho != 0.f && !inactive && logq[0] > -INFINITY) {
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < K; ++e) s += fast_ex2((logq[e] - logq[0]) * LOG2E);
-        const float l = logq[0] + fast_lg2(s) * LN2;
-#pragma unroll
-        for (int e = 0; e < K; ++e) logq[e] -= rho * l;
-    }
+    int content[K];
+    float weight[K];
+    thread_decode<T, U, P, K>(src, p.re_norm[which], content, weight);
     const int shift = (h < p.E) ? rn_pos_mod(p.pos[b * p.pb + t * p.pt], p.A) : 0;
     const int offs = (p.encode_batch ? (b * p.H + h) : h) * p.A;
     const int64_t o = b * p.ob + h * p.oh + t * p.ot + (which ? K : 0);
@@ -360,9 +46,8 @@ __global__ void __launch_bounds__(FAST_THREADS) rn_addr_fast_kernel(const FastPa
     float out_v[K];
 #pragma unroll
     for (int e = 0; e < K; ++e) {
-        const bool noop = inactive || logq[e] == -INFINITY;
-        out_i[e] = offs + rn_cape(noop ? e : beam_i[e], shift, p.A);
-        out_v[e] = inactive ? 0.f : p.sign[which] * fast_ex2(logq[e] * LOG2E);
+        out_i[e] = offs + rn_cape(content[e], shift, p.A);
+        out_v[e] = p.sign[which] * weight[e];
     }
 #pragma unroll
     for (int v = 0; v < K / 4; ++v) {

@@ -7,7 +7,7 @@
 //   optional head RMSNorm + sigmoid gate is applied before y is stored in the I/O dtype.
 //
 // State offsets are 64-bit: B*H*A*C may exceed 2^31 elements.
-#include "rn_addr.cuh"
+#include "rn_addr_fast.cuh"
 #include "rn_gsu.cuh"
 
 constexpr int RN_DEC_WARPS = 4;
@@ -193,6 +193,189 @@ __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDe
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// specialised decode step: 16 (b,h) pairs per CTA
+// ------------------------------------------------------------------------------------------
+// Warp 0 decodes the 32 addresses of the CTA (lanes 0-15 the write logits, 16-31 the read logits of
+// the 16 pairs) with the thread-per-row decoder, so the selection costs one warp-instruction per 32
+// addresses instead of one warp per address.  Then warp w owns pairs 2w and 2w+1: it loads the K
+// write rows of a pair at once (K 512-byte loads in flight), updates and stores them, then loads
+// the K read rows, reduces them in registers and applies the epilogue.  A lane always re-reads
+// exactly the 16 bytes of a row that it wrote itself, so no barrier separates writes from reads.
+constexpr int RN_DECF_PAIRS = 16;
+constexpr int RN_DECF_THREADS = 256;
+
+template <typename T, int U, int P, int K, int NV>
+__global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(const RnDecodeParams p) {
+    __shared__ int sel_slot[RN_DECF_PAIRS][2][K];
+    __shared__ float sel_val[RN_DECF_PAIRS][2][K];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int BH = p.B * p.H;
+    const int bh0 = blockIdx.x * RN_DECF_PAIRS;
+    const int C = p.C;
+
+    if (warp == 0) {
+        const int pair = lane & 15, which = lane >> 4;
+        const int bh = bh0 + pair;
+        if (bh < BH) {
+            const int b = bh / p.H, h = bh % p.H;
+            const T *src = static_cast<const T *>(which ? p.r_addr : p.w_addr) + int64_t(bh) * U * P;
+            int content[K];
+            float weight[K];
+            rn_fast::thread_decode<T, U, P, K>(src, p.re_norm[which], content, weight);
+            const int shift = (h < p.E) ? rn_pos_mod(p.pos[b], p.A) : 0;
+#pragma unroll
+            for (int e = 0; e < K; ++e) {
+                sel_slot[pair][which][e] = rn_cape(content[e], shift, p.A);
+                sel_val[pair][which][e] = weight[e];
+            }
+        }
+    }
+    __syncthreads();
+
+#pragma unroll 1
+    for (int pp = 0; pp < 2; ++pp) {
+        const int pair = warp * 2 + pp;
+        const int bh = bh0 + pair;
+        if (bh >= BH) break;
+        const int b = bh / p.H;
+        T *y = static_cast<T *>(p.y) + int64_t(bh) * C;
+        if (p.mask != nullptr && p.mask[b] == 0) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+            continue;
+        }
+        float *slot = p.slot + int64_t(bh) * p.A * C;
+        float *mass = p.mass + int64_t(bh) * p.A;
+        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[bh]);
+        float4 xv[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) xv[v] = rn_load4<T>(static_cast<const T *>(p.x) + int64_t(bh) * C + v * 128 + lane * 4);
+
+        // ---- writes -----------------------------------------------------------------------------
+        {
+            const int a_l = lane < K ? sel_slot[pair][0][lane] : 0;
+            const float w_l = lane < K ? sel_val[pair][0][lane] : 0.f;
+            float gain_l = 0.f;
+            float4 rows[K][NV];
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int a = __shfl_sync(RN_FULL, a_l, k);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
+            }
+            if (lane < K && w_l != 0.f) {
+                const RnGate g = rn_gate(w_l, gamma, mass[a_l], p.eps);
+                gain_l = g.gain;
+                mass[a_l] = g.mass;
+            }
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int a = __shfl_sync(RN_FULL, a_l, k);
+                const float w = __shfl_sync(RN_FULL, w_l, k);
+                const float gain = __shfl_sync(RN_FULL, gain_l, k);
+                if (w != 0.f) {
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        float4 s = rows[k][v];
+                        s.x = fmaf(gain, xv[v].x - s.x, s.x);
+                        s.y = fmaf(gain, xv[v].y - s.y, s.y);
+                        s.z = fmaf(gain, xv[v].z - s.z, s.z);
+                        s.w = fmaf(gain, xv[v].w - s.w, s.w);
+                        *reinterpret_cast<float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4) = s;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+
+        // ---- reads (after the writes of this step) ---------------------------------------------------
+        float4 acc[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float scale = 1.f;
+        {
+            const int a_l = lane < K ? sel_slot[pair][1][lane] : 0;
+            float r_l = lane < K ? sel_val[pair][1][lane] : 0.f;
+            float4 rows[K][NV];
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int a = __shfl_sync(RN_FULL, a_l, k);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
+            }
+            if (p.mass_aware) {
+                const float rm = (lane < K && r_l != 0.f) ? r_l * mass[a_l] : 0.f;
+                const float sr = rn_warp_sum(lane < K ? r_l : 0.f), srm = rn_warp_sum(rm);
+                scale = sr / (srm + p.eps);
+                r_l = rm;
+            }
+#pragma unroll
+            for (int k = K - 1; k >= 0; --k) {
+                const float coef = __shfl_sync(RN_FULL, r_l, k);
+                if (coef != 0.f) {
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        acc[v].x = fmaf(coef, rows[k][v].x, acc[v].x);
+                        acc[v].y = fmaf(coef, rows[k][v].y, acc[v].y);
+                        acc[v].z = fmaf(coef, rows[k][v].z, acc[v].z);
+                        acc[v].w = fmaf(coef, rows[k][v].w, acc[v].w);
+                    }
+                }
+            }
+        }
+        float sq = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            acc[v].x *= scale; acc[v].y *= scale; acc[v].z *= scale; acc[v].w *= scale;
+            sq += acc[v].x * acc[v].x + acc[v].y * acc[v].y + acc[v].z * acc[v].z + acc[v].w * acc[v].w;
+        }
+        if (p.norm_weight != nullptr) {
+            const float inv_rms = rsqrtf(rn_warp_sum(sq) / float(C) + p.norm_eps);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const float4 nw = *reinterpret_cast<const float4 *>(p.norm_weight + v * 128 + lane * 4);
+                acc[v].x *= inv_rms * nw.x; acc[v].y *= inv_rms * nw.y; acc[v].z *= inv_rms * nw.z; acc[v].w *= inv_rms * nw.w;
+            }
+        }
+        if (p.gate != nullptr) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + int64_t(bh) * C + v * 128 + lane * 4);
+                acc[v].x /= 1.f + expf(-gl.x); acc[v].y /= 1.f + expf(-gl.y);
+                acc[v].z /= 1.f + expf(-gl.z); acc[v].w /= 1.f + expf(-gl.w);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, acc[v]);
+    }
+}
+
+template <typename T, int U, int P, int K>
+static int rn_launch_decode_fast_c(const RnDecodeParams &p, cudaStream_t stream) {
+    const int grid = (p.B * p.H + RN_DECF_PAIRS - 1) / RN_DECF_PAIRS;
+    if (p.C == 128) rn_decode_fast_kernel<T, U, P, K, 1><<<grid, RN_DECF_THREADS, 0, stream>>>(p);
+    else if (p.C == 256) rn_decode_fast_kernel<T, U, P, K, 2><<<grid, RN_DECF_THREADS, 0, stream>>>(p);
+    else return -1;
+    return 0;
+}
+
+// 0 = launched, -1 = no specialised kernel for this shape
+template <typename T>
+static int rn_launch_decode_fast(const RnDecodeParams &p, cudaStream_t stream) {
+    if (p.K[0] != p.K[1]) return -1;
+    const size_t esz = sizeof(T);
+    const uintptr_t io = reinterpret_cast<uintptr_t>(p.w_addr) | reinterpret_cast<uintptr_t>(p.r_addr) |
+                         reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y) |
+                         reinterpret_cast<uintptr_t>(p.gate) | reinterpret_cast<uintptr_t>(p.norm_weight);
+    if ((io & 15) != 0 || (size_t(p.U) * p.P * esz) % 16 != 0) return -1;
+    if (p.U == 2 && p.P == 64 && p.K[0] == 16) return rn_launch_decode_fast_c<T, 2, 64, 16>(p, stream);
+    if (p.U == 3 && p.P == 32 && p.K[0] == 8) return rn_launch_decode_fast_c<T, 3, 32, 8>(p, stream);
+    if (p.U == 2 && p.P == 16 && p.K[0] == 4) return rn_launch_decode_fast_c<T, 2, 16, 4>(p, stream);
+    return -1;
+}
+
 static int rn_per_lane_dec(int64_t n) { return n <= 32 ? 1 : (n <= 64 ? 2 : 4); }
 
 template <typename T>
@@ -251,6 +434,14 @@ extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void
     int rc;
     rn_prof_reset();
     rn_prof_mark(cudaStream_t(stream));
+    rc = dtype == RN_F32 ? rn_launch_decode_fast<float>(p, cudaStream_t(stream))
+         : dtype == RN_F16 ? rn_launch_decode_fast<__half>(p, cudaStream_t(stream))
+                           : rn_launch_decode_fast<__nv_bfloat16>(p, cudaStream_t(stream));
+    if (rc == 0) {
+        RN_CUDA(cudaGetLastError());
+        rn_prof_mark(cudaStream_t(stream));
+        return 0;
+    }
     if (dtype == RN_F32) rc = rn_launch_decode<float>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
     else if (dtype == RN_F16) rc = rn_launch_decode<__half>(p, kpl, ppl, grid, smem, cudaStream_t(stream));
     else rc = rn_launch_decode<__nv_bfloat16>(p, kpl, ppl, grid, smem, cudaStream_t(stream));

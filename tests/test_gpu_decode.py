@@ -28,6 +28,9 @@ def _inputs(B, H, U, P, C, dtype, seed):
     (2, 3, 3, 8, 29, (8, 3), torch.float16),
     (1, 2, 4, 4, 7, (40, 33), torch.float32),
     (1, 2, 2, 64, 256, (16, 16), torch.bfloat16),
+    (3, 7, 2, 64, 128, (16, 16), torch.bfloat16),   # 21 pairs: a full and a partial CTA of the specialised kernel
+    (2, 4, 2, 16, 128, (4, 4), torch.float32),
+    (2, 2, 3, 32, 128, (8, 8), torch.float16),
 ])
 @pytest.mark.parametrize("mass_aware", [False, True])
 def test_decode_step_matches_oracle(B, H, U, P, C, K, dtype, mass_aware):
@@ -73,8 +76,8 @@ def test_decode_step_matches_reference_golden(name):
 
 def test_fused_epilogue_matches_oracle():
     ops()
-    B, H, U, P, C, K = 2, 4, 2, 16, 64, (4, 4)
-    for dtype in (torch.float32, torch.bfloat16):
+    for (B, H, U, P, C, K), dtype in (((2, 4, 2, 16, 64, (4, 4)), torch.float32), ((2, 4, 2, 16, 64, (4, 4)), torch.bfloat16),
+                                     ((2, 4, 2, 64, 128, (16, 16)), torch.bfloat16), ((1, 3, 2, 16, 128, (4, 4)), torch.float32)):
         w, r, x, g, slot, mass, pos = _inputs(B, H, U, P, C, dtype, 10)
         nw = randn((C,), 20) * 0.1 + 1.0
         gate = randn((B, H, C), 21, dtype)
