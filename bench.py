@@ -368,6 +368,53 @@ def cpu_baseline(reps=1):
                        f"scaled to {s['H']}-head tokens; {best:.2f} s")
 
 
+def run_ncu_case(name):
+    """Small single-GPU cases of the same kernels for profiler captures (a few GB at most, inputs
+    larger than L2): prints a short JSON and exits."""
+    import ramnet_ops  # noqa: F401
+    device = torch.device("cuda", 0)
+    ops = torch.ops.ramnet_ops
+    g = torch.Generator(device=device).manual_seed(0)
+    if name == "prefill_small":
+        B, T, H, U, P, K, C, E = 2, 4096, 16, 2, 64, 16, 128, 8
+        A = P ** U
+        q = torch.randn(B, T, H, U, P, device=device, generator=g).bfloat16()
+        k = torch.randn(B, T, H, U, P, device=device, generator=g).bfloat16()
+        v = torch.randn(B, T, H, C, device=device, generator=g).bfloat16()
+        gm = torch.sigmoid(torch.randn(B, T, H, device=device, generator=g) + 1).bfloat16()
+        pos = torch.arange(T, device=device, dtype=torch.int32).view(1, T).expand(B, T).contiguous()
+        slot0, mass0 = torch.zeros(B, H, A, C, device=device), torch.full((B, H, A), 1.0 / A, device=device)
+        for _ in range(3):
+            idx, val = ops.topk_addr_forward(k.permute(0, 2, 3, 4, 1), q.permute(0, 2, 3, 4, 1), E, A, pos, K, K, 0.0, 0.0)
+            y, s1, m1 = ops.gsu_forward(idx, val, v.permute(0, 2, 1, 3), gm.permute(0, 2, 1), slot0, mass0, None, K, K, False, 1e-12)
+        out = float(y.float().abs().mean())
+    elif name == "decode_small":
+        B, H, U, P, K, C, E = 64, 16, 2, 64, 16, 128, 8
+        A = P ** U
+        slot = torch.randn(B, H, A, C, device=device, generator=g) * 0.1
+        mass = torch.rand(B, H, A, device=device, generator=g) + 0.1
+        nomask = torch.empty(0, dtype=torch.bool, device=device)
+        pos = torch.zeros(B, device=device, dtype=torch.int32)
+        for _ in range(6):
+            q = torch.randn(B, H, U, P, device=device, generator=g).bfloat16()
+            k = torch.randn(B, H, U, P, device=device, generator=g).bfloat16()
+            v = torch.randn(B, H, C, device=device, generator=g).bfloat16()
+            gm = torch.sigmoid(torch.randn(B, H, device=device, generator=g)).bfloat16()
+            y = ops.topk_autoregressive_(k, q, v, gm, slot, mass, nomask, E, pos, K, K, 0.0, 0.0, False, 1e-12)
+        out = float(y.float().abs().mean())
+    else:
+        B, T, H, U, P, K, E = 2, 8192, 16, 3, 32, 8, 8
+        A = P ** U
+        q = (torch.randn(B, T, H, U, P, device=device, generator=g) * 1.5).bfloat16()
+        k = (torch.randn(B, T, H, U, P, device=device, generator=g) * 1.5).bfloat16()
+        pos = torch.arange(T, device=device, dtype=torch.int32).view(1, T).expand(B, T).contiguous()
+        for _ in range(3):
+            idx, val = ops.topk_addr_forward(k.permute(0, 2, 3, 4, 1), q.permute(0, 2, 3, 4, 1), E, A, pos, K, K, 0.0, 0.0)
+        out = float(val.abs().mean())
+    torch.cuda.synchronize()
+    print(json.dumps({"ncu_case": name, "checksum": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,12 +423,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill"])
     ap.add_argument("--no-extra", action="store_true", help="skip the decode and address-only measurements")
+    ap.add_argument("--ncu-case", default=None, choices=["prefill_small", "decode_small", "addr_small"],
+                    help="run one small case of the kernels (for profiler captures) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.ncu_case:
+        run_ncu_case(args.ncu_case)
+        return
 
     if args.impl == "reference":
         if rank != 0:
