@@ -12,6 +12,7 @@ template <typename T, bool SMEM_TABLES, int EPT>
 __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const RnGsuParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float gam[2][RN_GSU_LMAX];
+    __shared__ int n_chain, n_heads;
     __shared__ float tok_scale[RN_GSU_LMAX];
     __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
 
@@ -38,6 +39,10 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
     float *ev_c = ev_v + p.NE;
 
     if (bh == 0 && tid == 0) *p.status = 0;
+    if (tid == 0) {
+        n_chain = 0;
+        n_heads = 0;
+    }
     const float *mass_in = p.mass_in + int64_t(bh) * A;
     for (int a = tid; a < A; a += RN_GSU_THREADS) {
         if (SMEM_TABLES || mass_in != mass) mass[a] = mass_in[a];
@@ -159,20 +164,62 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
                 if (ev_t[j] < Lc && ev_k[j] >= p.Kw && er[j] >= 0) ec[j] *= tok_scale[ev_t[j]];
         }
 
-        // ---- the chunk record, in event order (coalesced) ------------------------------------------
+        // ---- chains: slots with two or more live events in this chunk ---------------------------
         unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
         uint32_t *o_meta = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES);
         float *o_coef = reinterpret_cast<float *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 4);
-        uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
+        uint16_t *o_chain = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
+        uint16_t *o_heads = o_chain + NEp;
+        uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 12);
+        uint32_t chained = 0;
+        // (1) later events publish the largest round of their slot
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+            if (er[j] >= 1) atomicMin(&claim[ea[j]], 0xfffffffeu - uint32_t(er[j]));
+        __syncthreads();
+        // (2) the first event of such a slot reserves the chain's range and leaves base | length << 16
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            if (er[j] != 0) continue;
+            const uint32_t c = claim[ea[j]];
+            if (c == 0xffffffffu) continue;
+            const int n = int(0xfffffffeu - c) + 1;
+            const int base = atomicAdd(&n_chain, n);
+            o_heads[atomicAdd(&n_heads, 1)] = uint16_t(base);
+            claim[ea[j]] = uint32_t(base) | (uint32_t(n) << 16);
+            o_chain[base] = uint16_t(ev_t[j] | (ev_k[j] << 6));
+            chained |= 1u << j;
+        }
+        __syncthreads();
+        // (3) the later events take their place in the chain
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            if (er[j] < 1) continue;
+            const uint32_t c = claim[ea[j]];
+            const int base = int(c & 0xffffu), n = int(c >> 16);
+            o_chain[base + er[j]] = uint16_t(ev_t[j] | (ev_k[j] << 6) | (er[j] == n - 1 ? 0x8000 : 0));
+            chained |= 1u << j;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+            if (chained & (1u << j)) claim[ea[j]] = 0xffffffffu;
+
+        // ---- the chunk record, in event order (coalesced) ------------------------------------------
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             const int e = j * RN_GSU_THREADS + tid;
             if (e < NEp) {
                 const bool dead = er[j] < 0;
-                o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead);
+                o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead) | ((chained & (1u << j)) ? RN_EV_CHAIN : 0u);
                 o_coef[e] = dead ? 0.f : ec[j];
                 if (p.wide) o_slot[e] = ea[j];
             }
+        }
+        if (tid == 0) {
+            reinterpret_cast<uint32_t *>(rec)[1] = uint32_t(n_heads);
+            n_chain = 0;
+            n_heads = 0;
         }
         if (tid == 0) *reinterpret_cast<uint32_t *>(rec) = uint32_t(R);
         if (p.prev_mass != nullptr) {
@@ -239,7 +286,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
         const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
+        const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 12);
         const int R = int(*reinterpret_cast<const uint32_t *>(rec));
 
         for (int i = tid; i < Lc * cs; i += RN_GSU_THREADS) {
@@ -318,14 +365,14 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
 // ------------------------------------------------------------------------------------------
 // fast apply kernel: C % 4 == 0, A <= 65536; slice state + streamed chunk records in shared memory.
 //
-// Token-major: the CTA's 512 threads are split into one group per token of the chunk; inside a
-// group, thread (q, sub) owns the events k = q, q + KL, ... of that token for the 4 channels
-// sub*4 .. sub*4+3 and keeps their (meta, coefficient) in registers for the whole chunk.  x[t] sits
-// in registers (prefetched one chunk ahead), the token's output accumulates in registers and is
-// combined across the group's k-lanes with shuffles in a fixed order: the only shared-memory
-// traffic per event is the slot row itself.  One CTA barrier per round.
+// Unchained events (the only live event of their slot in this chunk: no ordering constraint) are
+// handled token-major: the CTA's 512 threads are split into one group per token; thread (q, sub)
+// of a group owns the events k = q, q + KL, ... of that token for the 4 channels sub*4 .. sub*4+3,
+// with x[t] in registers (prefetched one chunk ahead) and the token's output accumulating in
+// registers.  Chained slots are walked in time order, one thread group per chain, in parallel
+// over chains; their reads go through a per-(token,k) buffer that the token's owners add in a
+// fixed order afterwards.  Three CTA barriers per chunk, whatever the chain lengths.
 // ------------------------------------------------------------------------------------------
-
 template <typename T, int CS, int EV>
 __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2) {
     constexpr int G = CS / 4;  // threads per event (one float4 of channels each)
@@ -336,23 +383,25 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     const int bh = blockIdx.x / p.nslices;
     const int b = bh / p.H, h = bh % p.H;
     const int tid = threadIdx.x;
-    const int C = p.C, A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, L = p.L;
+    const int C = p.C, A = p.A, Kw = p.Kw, Kr = p.Kr, KT = p.Kw + p.Kr, L = p.L;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);  // multiple of 4
-    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);  // header + meta + coef
+    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 12);  // header, meta, coef, chain, heads
 
     // thread -> (token of the chunk, k-lane, channel group)
     const int TPT = 1 << tpt_log2;          // threads per token (8, 16 or 32: a group never leaves its warp)
     const int KL = TPT / G;                 // k-lanes per token
-    const int tok = tid >> tpt_log2;
+    const int tok = tid >> tpt_log2;        // tokens >= L (surplus threads) take no token-major work
     const int w = tid & (TPT - 1);
     const int sub = w % G, q = w / G;
     const bool chan_ok = sub * 4 < cvalid;
 
-    // dynamic smem: rec[2][rec_stride] | S[A*CS]
+    // dynamic smem: rec[2][rec_stride] | S[A*CS] | xt[L*CS] | ylate[L*Kr*CS]
     const size_t rec_stride = (size_t(rec_copy) + 127) / 128 * 128;
     unsigned char *rec0 = dyn;
     float *S = reinterpret_cast<float *>(dyn + 2 * rec_stride);
+    float *xt = S + size_t(A) * CS;
+    float *ylate = xt + size_t(L) * CS;
 
     if (tid == 0) {
         rn_mbar_init(&mbar[0], 1);
@@ -415,48 +464,85 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
         const unsigned char *rec = rec0 + buf * rec_stride;
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
+        const uint16_t *e_chain = reinterpret_cast<const uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
+        const uint16_t *e_heads = e_chain + p.NEp;
+        const int n_heads = int(reinterpret_cast<const uint32_t *>(rec)[1]);
 
-        // this thread's events of the chunk
-        uint32_t m[EV];
-        float cf[EV];
+        // ---- unchained events, token-major ---------------------------------------------------------
         const bool tok_ok = tok < Lc;
+        if (q == 0 && tok < L) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        uint32_t late = 0;  // this thread's chained reads, added after the chain pass
 #pragma unroll
         for (int j = 0; j < EV; ++j) {
             const int k = q + j * KL;
-            m[j] = RN_EV_DEAD;
-            cf[j] = 0.f;
-            if (tok_ok && k < KT) {
-                m[j] = e_meta[tok * KT + k];
-                cf[j] = e_coef[tok * KT + k];
+            if (!tok_ok || k >= KT) continue;
+            const uint32_t m = e_meta[tok * KT + k];
+            if (m & RN_EV_DEAD) continue;
+            if (m & RN_EV_CHAIN) {
+                if (k >= Kw) late |= 1u << j;
+                continue;
+            }
+            const float cf = e_coef[tok * KT + k];
+            float *row = S + (m & 0xffffu) * CS + sub * 4;
+            float4 s = *reinterpret_cast<float4 *>(row);
+            if (k < Kw) {
+                s.x = fmaf(cf, xv.x - s.x, s.x);
+                s.y = fmaf(cf, xv.y - s.y, s.y);
+                s.z = fmaf(cf, xv.z - s.z, s.z);
+                s.w = fmaf(cf, xv.w - s.w, s.w);
+                *reinterpret_cast<float4 *>(row) = s;
+            } else {
+                acc.x = fmaf(cf, s.x, acc.x);
+                acc.y = fmaf(cf, s.y, acc.y);
+                acc.z = fmaf(cf, s.z, acc.z);
+                acc.w = fmaf(cf, s.w, acc.w);
             }
         }
+        __syncthreads();  // x tile complete (chains touch other slots than the unchained events)
 
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < R; ++r) {
-#pragma unroll
-            for (int j = 0; j < EV; ++j) {
-                // live event of this round?  (dead events carry bit 24, so the compare fails)
-                if (((m[j] >> 16) & 0x1ffu) != uint32_t(r)) continue;
-                float *row = S + (m[j] & 0xffffu) * CS + sub * 4;
-                float4 s = *reinterpret_cast<float4 *>(row);
-                if (q + j * KL < Kw) {
-                    s.x = fmaf(cf[j], xv.x - s.x, s.x);
-                    s.y = fmaf(cf[j], xv.y - s.y, s.y);
-                    s.z = fmaf(cf[j], xv.z - s.z, s.z);
-                    s.w = fmaf(cf[j], xv.w - s.w, s.w);
-                    *reinterpret_cast<float4 *>(row) = s;
-                } else {
-                    acc.x = fmaf(cf[j], s.x, acc.x);
-                    acc.y = fmaf(cf[j], s.y, acc.y);
-                    acc.z = fmaf(cf[j], s.z, acc.z);
-                    acc.w = fmaf(cf[j], s.w, acc.w);
+        // ---- chains: one thread group per chained slot, events in time order -------------------------
+        {
+            const int csub = tid % G;
+            for (int c = tid / G; c < n_heads; c += RN_APPLY_THREADS / G) {
+                int pos = e_heads[c];
+                float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+                float *row = nullptr;
+                for (;;) {
+                    const uint32_t ce = e_chain[pos];
+                    const int ct = int(ce & 63u), ck = int((ce >> 6) & 255u);
+                    const int e = ct * KT + ck;
+                    const float cf = e_coef[e];
+                    if (row == nullptr) {
+                        row = S + (e_meta[e] & 0xffffu) * CS + csub * 4;
+                        s = *reinterpret_cast<float4 *>(row);
+                    }
+                    if (ck < Kw) {
+                        const float4 xr = *reinterpret_cast<const float4 *>(xt + ct * CS + csub * 4);
+                        s.x = fmaf(cf, xr.x - s.x, s.x);
+                        s.y = fmaf(cf, xr.y - s.y, s.y);
+                        s.z = fmaf(cf, xr.z - s.z, s.z);
+                        s.w = fmaf(cf, xr.w - s.w, s.w);
+                    } else {
+                        *reinterpret_cast<float4 *>(ylate + (ct * Kr + (ck - Kw)) * CS + csub * 4) =
+                            make_float4(cf * s.x, cf * s.y, cf * s.z, cf * s.w);
+                    }
+                    ++pos;
+                    if (ce & 0x8000u) break;
                 }
+                *reinterpret_cast<float4 *>(row) = s;  // the row stays in registers along the chain
             }
-            __syncthreads();
         }
+        __syncthreads();
 
-        // combine the k-lanes of the token (lanes w = q*G + sub of one warp when TPT <= 32)
+        // ---- chained reads of this thread's token, then combine the k-lanes ----------------------------
+#pragma unroll
+        for (int j = 0; j < EV; ++j) {
+            if (!(late & (1u << j))) continue;
+            const int k = q + j * KL;
+            const float4 v = *reinterpret_cast<const float4 *>(ylate + (tok * Kr + (k - Kw)) * CS + sub * 4);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
         for (int off = G; off < TPT; off <<= 1) {
             acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
             acc.y += __shfl_xor_sync(RN_FULL, acc.y, off);
@@ -480,16 +566,17 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
 // ------------------------------------------------------------------------------------------
 constexpr size_t RN_SMEM_BUDGET = 225 * 1024;
 
-static size_t rn_fast_smem(int64_t A, int cs, int NEp) {
-    const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 8, 128);
-    return 2 * rec_stride + size_t(A) * cs * 4;
+static size_t rn_fast_smem(int64_t A, int cs, int NEp, int L, int64_t Kr) {
+    const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 12, 128);
+    return 2 * rec_stride + (size_t(A) * cs + size_t(L) * cs + size_t(L) * Kr * cs) * 4;
 }
 
-// fast kernel geometry: 512 threads / next_pow2(L) tokens; events per thread (power of two) or 0 if > 16
-static int rn_fast_geometry(int L, int KT, int cs, int *tpt_log2) {
+// fast kernel geometry: threads / next_pow2(L) tokens; events per thread (power of two) or 0 if > 16
+static int rn_fast_geometry(int threads, int L, int KT, int cs, int *tpt_log2) {
     int lp = 1;
     while (lp < L) lp <<= 1;
-    int tpt = 512 / lp, lg = 0;
+    int tpt = threads / lp, lg = 0;
+    if (tpt > 32) tpt = 32;  // a token's group stays inside one warp; surplus threads idle
     while ((1 << lg) < tpt) ++lg;
     *tpt_log2 = lg;
     const int G = cs / 4;
@@ -517,7 +604,7 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     pl->smem_tables = (size_t(A) * 8 + ev_bytes) <= RN_SMEM_BUDGET;
     pl->sched_smem = rn_align((pl->smem_tables ? size_t(A) * 8 : 0) + ev_bytes, 16);
     pl->wide = A > 65536;
-    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 12 : 8), 128));
+    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 16 : 12), 128));
 
     // apply kernel: channels per CTA.  Largest slice that still gives two CTAs per SM of work,
     // else the smallest one (most parallelism).
@@ -526,8 +613,10 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     int best = 0;
     for (int cs = 4; cs <= (fast_ok ? 32 : 128); cs *= 2) {
         int lg = 0;
-        if (fast_ok && rn_fast_geometry(pl->L, int(Kw + Kr), cs, &lg) == 0) break;
-        const size_t need = fast_ok ? rn_fast_smem(A, cs, pl->NEp)
+        if (fast_ok && (rn_fast_geometry(RN_APPLY_THREADS, pl->L, int(Kw + Kr), cs, &lg) == 0 ||
+                        rn_fast_geometry(RN_SWEEP_THREADS, pl->L, int(Kw + Kr), cs, &lg) == 0))
+            break;
+        const size_t need = fast_ok ? rn_fast_smem(A, cs, pl->NEp, pl->L, Kr)
                                     : (size_t(A) * cs + size_t(pl->L) * cs + size_t(pl->L) * Kr * cs) * 4;
         if (need > RN_SMEM_BUDGET) break;
         const int64_t ncta = B * H * ((C + cs - 1) / cs);
@@ -538,9 +627,12 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
         pl->cs = best;
         pl->state_in_smem = 1;
         pl->fast = fast_ok;
-        pl->apply_smem = fast_ok ? rn_fast_smem(A, best, pl->NEp)
+        pl->apply_smem = fast_ok ? rn_fast_smem(A, best, pl->NEp, pl->L, Kr)
                                  : (size_t(A) * best + size_t(pl->L) * best + size_t(pl->L) * Kr * best) * 4;
-        if (fast_ok) pl->ev = rn_fast_geometry(pl->L, int(Kw + Kr), best, &pl->tpt_log2);
+        if (fast_ok) {
+            pl->ev = rn_fast_geometry(RN_APPLY_THREADS, pl->L, int(Kw + Kr), best, &pl->tpt_log2);
+            pl->evb = rn_fast_geometry(RN_SWEEP_THREADS, pl->L, int(Kw + Kr), best, &pl->tptb_log2);
+        }
     } else {
         // slot state stays in global memory; keep the per-CTA read buffer small
         int cs = 4;

@@ -18,11 +18,17 @@
 //
 // Chunk record (global workspace, 16-byte aligned, fixed size per call); entry e = t * (Kw+Kr) + k
 // keeps the order of the decoded addresses, so the record is written and read coalesced:
-//   u32 header[4]:  [0] = R, the number of rounds of this chunk
+//   u32 header[4]:  [0] = R, the number of rounds of this chunk; [1] = number of chains
 //   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-23 round, 24 dead (no-op event:
-//                   zero weight or masked token)
+//                   zero weight or masked token), 25 chained (its slot has >= 2 live events here)
 //   f32 coef[NEp]:  gain of a write / weight of a read (mass-aware scaling folded in)
+//   u16 chain[NEp]: the events of every chained slot, consecutive and in time order; an entry is
+//                   token | k << 6 | last-of-its-chain << 15
+//   u16 heads[NEp]: first chain[] position of each chain
 //   u32 slot[NEp]:  only in the wide format (A > 65536)
+// The fast apply kernel handles unchained events token-major and walks each chain with one
+// thread group, so it needs no per-round barriers; the generic kernel and the backward sweeps go
+// round by round.
 #pragma once
 
 #include "rn_common.cuh"
@@ -35,6 +41,7 @@ constexpr int RN_GSU_RMAX = 2 * RN_GSU_LMAX;      // most rounds in a chunk
 constexpr int RN_GSU_HDR_BYTES = 16;
 
 constexpr uint32_t RN_EV_DEAD = 1u << 24;
+constexpr uint32_t RN_EV_CHAIN = 1u << 25;
 
 __host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int round, bool dead) {
     return (slot16 & 0xffffu) | (uint32_t(round & 0xff) << 16) | (dead ? RN_EV_DEAD : 0u);
@@ -82,7 +89,8 @@ __host__ __device__ inline int rn_gsu_chunk_len(int Kw, int Kr) {
 }
 
 // ---- launch plan shared by the forward and backward entry points ---------------------------------
-constexpr int RN_APPLY_THREADS = 512;
+constexpr int RN_APPLY_THREADS = 1024;  // forward apply kernel
+constexpr int RN_SWEEP_THREADS = 512;   // backward replay / reverse kernels
 
 struct RnGsuPlan {
     int L, nchunks, NE, NEp, ept;
@@ -91,7 +99,8 @@ struct RnGsuPlan {
     int wide;              // A > 65536: records carry a separate slot array
     int64_t rec_bytes;
     int fast;              // fast apply kernel (C % 4 == 0, narrow records, state in shared memory)
-    int tpt_log2, ev;      // fast kernel: threads per token, events per thread
+    int tpt_log2, ev;      // fast apply kernel: threads per token, events per thread
+    int tptb_log2, evb;    // backward sweep kernels (RN_SWEEP_THREADS threads)
     int cs, nslices, state_in_smem;
     size_t apply_smem;
     // workspace layout (byte offsets)

@@ -41,7 +41,7 @@ __device__ __forceinline__ float rn_group_sum(float v, int G, unsigned mask) {
 // replay / reverse kernels (token-major, see rn_gsu_apply_fast_kernel)
 // ------------------------------------------------------------------------------------------
 template <typename T, int CS, int EV, bool REVERSE>
-__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2) {
+__global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2) {
     constexpr int G = CS / 4;
     const RnGsuParams &p = bp.f;
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     }
     {
         const float *src = (REVERSE ? bp.dslot_post : p.slot_in) + int64_t(bh) * A * C + c0;
-        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
+        for (int i = tid; i < A * G; i += RN_SWEEP_THREADS) {
             const int a = i / G, sg = i - a * G;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (sg * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sg * 4);
@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     if (REVERSE) {
         __syncthreads();
         float *dst = bp.dslot_out + int64_t(bh) * A * C + c0;
-        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
+        for (int i = tid; i < A * G; i += RN_SWEEP_THREADS) {
             const int a = i / G, sg = i - a * G;
             if (sg * 4 < cvalid)
                 *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sg * 4);
@@ -374,17 +374,17 @@ template <typename T, bool REVERSE>
 static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaStream_t stream) {
     const int grid = bp.f.B * bp.f.H * pl.nslices;
 #define RN_CASE(CSV, EVV)                                                                                            \
-    if (pl.cs == CSV && pl.ev == EVV) {                                                                              \
+    if (pl.cs == CSV && pl.evb == EVV) {                                                                              \
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE>,                                  \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, int(pl.apply_smem)));              \
-        rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE><<<grid, RN_APPLY_THREADS, pl.apply_smem, stream>>>(bp, pl.tpt_log2); \
+        rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE><<<grid, RN_SWEEP_THREADS, pl.apply_smem, stream>>>(bp, pl.tptb_log2); \
         return 0;                                                                                                    \
     }
 #define RN_CASES(CSV) RN_CASE(CSV, 1) RN_CASE(CSV, 2) RN_CASE(CSV, 4) RN_CASE(CSV, 8) RN_CASE(CSV, 16)
     RN_CASES(4) RN_CASES(8) RN_CASES(16) RN_CASES(32)
 #undef RN_CASES
 #undef RN_CASE
-    rn_set_error("no backward kernel for %d channels per CTA, %d events per thread", pl.cs, pl.ev);
+    rn_set_error("no backward kernel for %d channels per CTA, %d events per thread", pl.cs, pl.evb);
     return 1;
 }
 
