@@ -12,7 +12,7 @@ template <typename T, bool SMEM_TABLES, int EPT>
 __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const RnGsuParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float gam[2][RN_GSU_LMAX];
-    __shared__ int n_chain, n_heads;
+    __shared__ int hist[RN_GSU_RMAX + 3];
     __shared__ float tok_scale[RN_GSU_LMAX];
     __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
 
@@ -39,10 +39,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
     float *ev_c = ev_v + p.NE;
 
     if (bh == 0 && tid == 0) *p.status = 0;
-    if (tid == 0) {
-        n_chain = 0;
-        n_heads = 0;
-    }
+
     const float *mass_in = p.mass_in + int64_t(bh) * A;
     for (int a = tid; a < A; a += RN_GSU_THREADS) {
         if (SMEM_TABLES || mass_in != mass) mass[a] = mass_in[a];
@@ -164,46 +161,53 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
                 if (ev_t[j] < Lc && ev_k[j] >= p.Kw && er[j] >= 0) ec[j] *= tok_scale[ev_t[j]];
         }
 
-        // ---- chains: slots with two or more live events in this chunk ---------------------------
+        // ---- events of round >= 1, counting-sorted by round (warp-aggregated atomics) ------------
         unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
+        uint16_t *o_off = reinterpret_cast<uint16_t *>(rec + 8);  // o_off[r], r = 1 .. R
         uint32_t *o_meta = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES);
         float *o_coef = reinterpret_cast<float *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 4);
-        uint16_t *o_chain = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
-        uint16_t *o_heads = o_chain + NEp;
-        uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 12);
-        uint32_t chained = 0;
-        // (1) later events publish the largest round of their slot
-#pragma unroll
-        for (int j = 0; j < EPT; ++j)
-            if (er[j] >= 1) atomicMin(&claim[ea[j]], 0xfffffffeu - uint32_t(er[j]));
+        uint16_t *o_late = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
+        uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 10);
+        for (int r = tid; r < R + 2; r += RN_GSU_THREADS) hist[r] = 0;
         __syncthreads();
-        // (2) the first event of such a slot reserves the chain's range and leaves base | length << 16
+        const int lane = tid & 31;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            if (er[j] != 0) continue;
-            const uint32_t c = claim[ea[j]];
-            if (c == 0xffffffffu) continue;
-            const int n = int(0xfffffffeu - c) + 1;
-            const int base = atomicAdd(&n_chain, n);
-            o_heads[atomicAdd(&n_heads, 1)] = uint16_t(base);
-            claim[ea[j]] = uint32_t(base) | (uint32_t(n) << 16);
-            o_chain[base] = uint16_t(ev_t[j] | (ev_k[j] << 6));
-            chained |= 1u << j;
+            const bool emit = er[j] >= 1;
+            const unsigned act = __ballot_sync(RN_FULL, emit);
+            if (emit) {
+                const unsigned grp = __match_any_sync(act, er[j]);
+                if (lane == __ffs(grp) - 1) atomicAdd(&hist[er[j] + 1], __popc(grp));
+            }
         }
         __syncthreads();
-        // (3) the later events take their place in the chain
+        if (tid == 0) {
+            int acc = 0;
+            for (int r = 1; r <= R; ++r) {   // hist[r + 1] holds the count of round r
+                const int cnt = hist[r + 1];
+                hist[r] = acc;               // first entry of round r
+                acc += cnt;
+            }
+            hist[R] = acc;                   // rounds run 0 .. R-1: hist[R] = n_late
+            reinterpret_cast<uint32_t *>(rec)[0] = uint32_t(R);
+            reinterpret_cast<uint32_t *>(rec)[1] = uint32_t(acc);
+        }
+        __syncthreads();
+        for (int r = 1 + tid; r <= R; r += RN_GSU_THREADS) o_off[r] = uint16_t(hist[r]);
+        __syncthreads();
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            if (er[j] < 1) continue;
-            const uint32_t c = claim[ea[j]];
-            const int base = int(c & 0xffffu), n = int(c >> 16);
-            o_chain[base + er[j]] = uint16_t(ev_t[j] | (ev_k[j] << 6) | (er[j] == n - 1 ? 0x8000 : 0));
-            chained |= 1u << j;
+            const bool emit = er[j] >= 1;
+            const unsigned act = __ballot_sync(RN_FULL, emit);
+            if (emit) {
+                const unsigned grp = __match_any_sync(act, er[j]);
+                const int leader = __ffs(grp) - 1;
+                int base = 0;
+                if (lane == leader) base = atomicAdd(&hist[er[j]], __popc(grp));
+                base = __shfl_sync(grp, base, leader);
+                o_late[base + __popc(grp & ((1u << lane) - 1u))] = uint16_t(ev_t[j] | (ev_k[j] << 6));
+            }
         }
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < EPT; ++j)
-            if (chained & (1u << j)) claim[ea[j]] = 0xffffffffu;
 
         // ---- the chunk record, in event order (coalesced) ------------------------------------------
 #pragma unroll
@@ -211,17 +215,11 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
             const int e = j * RN_GSU_THREADS + tid;
             if (e < NEp) {
                 const bool dead = er[j] < 0;
-                o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead) | ((chained & (1u << j)) ? RN_EV_CHAIN : 0u);
+                o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead);
                 o_coef[e] = dead ? 0.f : ec[j];
                 if (p.wide) o_slot[e] = ea[j];
             }
         }
-        if (tid == 0) {
-            reinterpret_cast<uint32_t *>(rec)[1] = uint32_t(n_heads);
-            n_chain = 0;
-            n_heads = 0;
-        }
-        if (tid == 0) *reinterpret_cast<uint32_t *>(rec) = uint32_t(R);
         if (p.prev_mass != nullptr) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
@@ -286,7 +284,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
         const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 12);
+        const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 10);
         const int R = int(*reinterpret_cast<const uint32_t *>(rec));
 
         for (int i = tid; i < Lc * cs; i += RN_GSU_THREADS) {
@@ -365,13 +363,13 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
 // ------------------------------------------------------------------------------------------
 // fast apply kernel: C % 4 == 0, A <= 65536; slice state + streamed chunk records in shared memory.
 //
-// Unchained events (the only live event of their slot in this chunk: no ordering constraint) are
-// handled token-major: the CTA's 512 threads are split into one group per token; thread (q, sub)
-// of a group owns the events k = q, q + KL, ... of that token for the 4 channels sub*4 .. sub*4+3,
-// with x[t] in registers (prefetched one chunk ahead) and the token's output accumulating in
-// registers.  Chained slots are walked in time order, one thread group per chain, in parallel
-// over chains; their reads go through a per-(token,k) buffer that the token's owners add in a
-// fixed order afterwards.  Three CTA barriers per chunk, whatever the chain lengths.
+// Round 0 (the first live event of every slot in the chunk, ~80 % of the events) is applied
+// token-major: the CTA's threads are split into one group per token; thread (q, sub) of a group
+// owns the events k = q, q + KL, ... of that token for the 4 channels sub*4 .. sub*4+3, with x[t] in
+// registers (prefetched one chunk ahead) and the token's output accumulating in registers.  The
+// later rounds are sparse; they are applied from the round-sorted late[] list, one (event, channel
+// group) per thread, so the lanes stay dense; their reads go through a per-(token,k) buffer that
+// the token's owners add in a fixed order afterwards.  One CTA barrier per round.
 // ------------------------------------------------------------------------------------------
 template <typename T, int CS, int EV>
 __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2) {
@@ -386,7 +384,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     const int C = p.C, A = p.A, Kw = p.Kw, Kr = p.Kr, KT = p.Kw + p.Kr, L = p.L;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);  // multiple of 4
-    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 12);  // header, meta, coef, chain, heads
+    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 10);  // header, meta, coef, late
 
     // thread -> (token of the chunk, k-lane, channel group)
     const int TPT = 1 << tpt_log2;          // threads per token (8, 16 or 32: a group never leaves its warp)
@@ -464,23 +462,22 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
         const unsigned char *rec = rec0 + buf * rec_stride;
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const uint16_t *e_chain = reinterpret_cast<const uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
-        const uint16_t *e_heads = e_chain + p.NEp;
-        const int n_heads = int(reinterpret_cast<const uint32_t *>(rec)[1]);
+        const uint16_t *e_late = reinterpret_cast<const uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
+        const uint16_t *late_off = reinterpret_cast<const uint16_t *>(rec + 8);
+        const int R = int(reinterpret_cast<const uint32_t *>(rec)[0]);
 
-        // ---- unchained events, token-major ---------------------------------------------------------
+        // ---- round 0, token-major ----------------------------------------------------------------------
         const bool tok_ok = tok < Lc;
         if (q == 0 && tok < L) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        uint32_t late = 0;  // this thread's chained reads, added after the chain pass
+        uint32_t late = 0;  // this thread's reads of later rounds, added after those rounds
 #pragma unroll
         for (int j = 0; j < EV; ++j) {
             const int k = q + j * KL;
             if (!tok_ok || k >= KT) continue;
             const uint32_t m = e_meta[tok * KT + k];
-            if (m & RN_EV_DEAD) continue;
-            if (m & RN_EV_CHAIN) {
-                if (k >= Kw) late |= 1u << j;
+            if (m & (RN_EV_DEAD | 0x00ff0000u)) {  // dead, or a later round
+                if (!(m & RN_EV_DEAD) && k >= Kw) late |= 1u << j;
                 continue;
             }
             const float cf = e_coef[tok * KT + k];
@@ -499,43 +496,37 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
                 acc.w = fmaf(cf, s.w, acc.w);
             }
         }
-        __syncthreads();  // x tile complete (chains touch other slots than the unchained events)
+        __syncthreads();
 
-        // ---- chains: one thread group per chained slot, events in time order -------------------------
+        // ---- rounds 1 .. R-1 from the list: thread -> (entry, channel group) ----------------------------
         {
             const int csub = tid % G;
-            for (int c = tid / G; c < n_heads; c += RN_APPLY_THREADS / G) {
-                int pos = e_heads[c];
-                float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-                float *row = nullptr;
-                for (;;) {
-                    const uint32_t ce = e_chain[pos];
-                    const int ct = int(ce & 63u), ck = int((ce >> 6) & 255u);
+            for (int r = 1; r < R; ++r) {
+                const int beg = late_off[r], end = late_off[r + 1];
+                for (int i = beg + tid / G; i < end; i += RN_APPLY_THREADS / G) {
+                    const uint32_t ce = e_late[i];
+                    const int ct = int(ce & 63u), ck = int(ce >> 6);
                     const int e = ct * KT + ck;
                     const float cf = e_coef[e];
-                    if (row == nullptr) {
-                        row = S + (e_meta[e] & 0xffffu) * CS + csub * 4;
-                        s = *reinterpret_cast<float4 *>(row);
-                    }
+                    float *row = S + (e_meta[e] & 0xffffu) * CS + csub * 4;
+                    float4 s = *reinterpret_cast<float4 *>(row);
                     if (ck < Kw) {
                         const float4 xr = *reinterpret_cast<const float4 *>(xt + ct * CS + csub * 4);
                         s.x = fmaf(cf, xr.x - s.x, s.x);
                         s.y = fmaf(cf, xr.y - s.y, s.y);
                         s.z = fmaf(cf, xr.z - s.z, s.z);
                         s.w = fmaf(cf, xr.w - s.w, s.w);
+                        *reinterpret_cast<float4 *>(row) = s;
                     } else {
                         *reinterpret_cast<float4 *>(ylate + (ct * Kr + (ck - Kw)) * CS + csub * 4) =
                             make_float4(cf * s.x, cf * s.y, cf * s.z, cf * s.w);
                     }
-                    ++pos;
-                    if (ce & 0x8000u) break;
                 }
-                *reinterpret_cast<float4 *>(row) = s;  // the row stays in registers along the chain
+                __syncthreads();
             }
         }
-        __syncthreads();
 
-        // ---- chained reads of this thread's token, then combine the k-lanes ----------------------------
+        // ---- later-round reads of this thread's token, then combine the k-lanes ----------------------------
 #pragma unroll
         for (int j = 0; j < EV; ++j) {
             if (!(late & (1u << j))) continue;
@@ -567,7 +558,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
 constexpr size_t RN_SMEM_BUDGET = 225 * 1024;
 
 static size_t rn_fast_smem(int64_t A, int cs, int NEp, int L, int64_t Kr) {
-    const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 12, 128);
+    const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 10, 128);
     return 2 * rec_stride + (size_t(A) * cs + size_t(L) * cs + size_t(L) * Kr * cs) * 4;
 }
 
@@ -597,14 +588,14 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     pl->L = rn_gsu_chunk_len(int(Kw), int(Kr));
     pl->nchunks = int((T + pl->L - 1) / pl->L);
     pl->NE = pl->L * int(Kw + Kr);
-    pl->NEp = int(rn_align(pl->NE, 4));
+    pl->NEp = int(rn_align(pl->NE, 8));
     int ept = (pl->NE + RN_GSU_THREADS - 1) / RN_GSU_THREADS;
     pl->ept = ept <= 1 ? 1 : (ept <= 2 ? 2 : (ept <= 4 ? 4 : (ept <= 8 ? 8 : 16)));
     const size_t ev_bytes = size_t(pl->NE) * 8 + 16;  // mass-aware per-event scratch
     pl->smem_tables = (size_t(A) * 8 + ev_bytes) <= RN_SMEM_BUDGET;
     pl->sched_smem = rn_align((pl->smem_tables ? size_t(A) * 8 : 0) + ev_bytes, 16);
     pl->wide = A > 65536;
-    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 16 : 12), 128));
+    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 14 : 10), 128));
 
     // apply kernel: channels per CTA.  Largest slice that still gives two CTAs per SM of work,
     // else the smallest one (most parallelism).

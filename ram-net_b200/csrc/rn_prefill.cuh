@@ -18,17 +18,15 @@
 //
 // Chunk record (global workspace, 16-byte aligned, fixed size per call); entry e = t * (Kw+Kr) + k
 // keeps the order of the decoded addresses, so the record is written and read coalesced:
-//   u32 header[4]:  [0] = R, the number of rounds of this chunk; [1] = number of chains
+//   header (272 bytes): u32 R (rounds of this chunk), u32 n_late, then u16 late_off[r] for
+//                   r = 1 .. R: first late[] entry of round r (late_off[R] = n_late)
 //   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-23 round, 24 dead (no-op event:
-//                   zero weight or masked token), 25 chained (its slot has >= 2 live events here)
+//                   zero weight or masked token)
 //   f32 coef[NEp]:  gain of a write / weight of a read (mass-aware scaling folded in)
-//   u16 chain[NEp]: the events of every chained slot, consecutive and in time order; an entry is
-//                   token | k << 6 | last-of-its-chain << 15
-//   u16 heads[NEp]: first chain[] position of each chain
+//   u16 late[NEp]:  the events of round >= 1, sorted by round; an entry is token | k << 6
 //   u32 slot[NEp]:  only in the wide format (A > 65536)
-// The fast apply kernel handles unchained events token-major and walks each chain with one
-// thread group, so it needs no per-round barriers; the generic kernel and the backward sweeps go
-// round by round.
+// Round 0 holds ~80 % of the events of a chunk and is applied token-major (dense); the later,
+// sparse rounds are applied from the late[] list so every lane has work.
 #pragma once
 
 #include "rn_common.cuh"
@@ -38,10 +36,9 @@ constexpr int RN_GSU_THREADS = 256;               // schedule kernel and generic
 constexpr int RN_GSU_LMAX = 64;                   // longest time chunk
 constexpr int RN_GSU_NE_MAX = 4096;               // most events per chunk (L * (Kw + Kr))
 constexpr int RN_GSU_RMAX = 2 * RN_GSU_LMAX;      // most rounds in a chunk
-constexpr int RN_GSU_HDR_BYTES = 16;
+constexpr int RN_GSU_HDR_BYTES = 272;            // 8 + 2 * (RN_GSU_RMAX + 2), rounded up to 16
 
 constexpr uint32_t RN_EV_DEAD = 1u << 24;
-constexpr uint32_t RN_EV_CHAIN = 1u << 25;
 
 __host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int round, bool dead) {
     return (slot16 & 0xffffu) | (uint32_t(round & 0xff) << 16) | (dead ? RN_EV_DEAD : 0u);
