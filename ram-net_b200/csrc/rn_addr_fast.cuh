@@ -339,4 +339,155 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
     }
 }
 
+// ---- four lanes per row ------------------------------------------------------------------------
+// Same result as thread_decode, but the work of one row is spread over four adjacent lanes so the
+// dependent instruction chain is ~5x shorter (used where few rows must finish quickly: the decode
+// step).  Needs P == 4 * K: each lane sorts K logits of a digit, then two cross-lane folds
+// (xor 1, xor 2) leave the digit's sorted Top-K in all four lanes; candidate blocks of a level are
+// built one per lane and folded the same way.  Every lane of the warp must call it.
+__device__ __forceinline__ Key32 key_shfl_xor(const Key32 &k, int m) { return Key32{__shfl_xor_sync(RN_FULL, k.v, m)}; }
+__device__ __forceinline__ Key64 key_shfl_xor(const Key64 &k, int m) {
+    return Key64{__shfl_xor_sync(RN_FULL, k.hi, m), __shfl_xor_sync(RN_FULL, k.lo, m)};
+}
+template <int K, typename Key>
+__device__ __forceinline__ void fold_topk_xlane(Key *a, int m) {
+    Key t[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) t[i] = key_max(a[i], key_shfl_xor(a[K - 1 - i], m));
+#pragma unroll
+    for (int i = 0; i < K; ++i) a[i] = t[i];
+    bitonic_merge_desc<K>(a);
+}
+
+template <typename T, int K>
+__device__ __forceinline__ void quad_make_keys(const T *src, int p0, Key64 *dk) {
+    rn_for_each_logit<T, K>(src, [&](int q, float x) { dk[q] = Key64{rn_ord(x + 0.0f), ~uint32_t(p0 + q)}; });
+}
+template <typename T, int K>
+__device__ __forceinline__ void quad_make_keys(const T *src, int p0, Key32 *dk) {
+    if constexpr (K >= 8) {
+#pragma unroll
+        for (int v = 0; v < K / 8; ++v) {
+            const uint4 raw = reinterpret_cast<const uint4 *>(src)[v];
+            const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int q = 8 * v + 2 * c;
+                dk[q] = Key32{(ord16_from_bf16(wds[c] & 0xffffu) << 16) | (0xffffu - uint32_t(p0 + q))};
+                dk[q + 1] = Key32{(ord16_from_bf16(wds[c] >> 16) << 16) | (0xffffu - uint32_t(p0 + q + 1))};
+            }
+        }
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(src);  // K == 4 sixteen-bit logits
+        const uint32_t wds[2] = {raw.x, raw.y};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            dk[2 * c] = Key32{(ord16_from_bf16(wds[c] & 0xffffu) << 16) | (0xffffu - uint32_t(p0 + 2 * c))};
+            dk[2 * c + 1] = Key32{(ord16_from_bf16(wds[c] >> 16) << 16) | (0xffffu - uint32_t(p0 + 2 * c + 1))};
+        }
+    }
+}
+
+template <typename T, int U, int P, int K>
+__device__ __forceinline__ void quad_decode(const T *src, const float rho, const int gl, int (&content)[K],
+                                            float (&weight)[K]) {
+    using DKey = typename std::conditional<Raw<T>::wide, Key64, Key32>::type;
+    constexpr float LOG2E = 1.4426950408889634f;
+    constexpr float LN2 = 0.6931471805599453f;
+    static_assert(P == 4 * K && (K & (K - 1)) == 0 && K >= 4, "quad_decode needs P == 4 K");
+    constexpr int NREM = rn_remainder_count(K);
+    constexpr int NBLK = (NREM + K - 1) / K;
+    static_assert(NBLK <= 2, "candidate blocks must fit the four lanes");
+
+    float beam_s[K];
+    int beam_i[K];
+    float lse_total = 0.f;
+    bool inactive = false;
+    int stride = 1;
+
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const T *mine = src + u * P + gl * K;  // this lane's K logits of digit u
+        DKey dk[K];
+        quad_make_keys<T, K>(mine, gl * K, dk);
+        oem_sort_desc<K>(dk);
+        fold_topk_xlane<K>(dk, 1);
+        fold_topk_xlane<K>(dk, 2);
+        // dk[0..K) = the digit's K best logits, sorted, in all four lanes
+        const float xmax = digit_value<T>(dk[0]);
+        if (xmax == -INFINITY) {
+            inactive = true;
+        } else {
+            float s = 0.f;
+            const float off = xmax * LOG2E;
+            if constexpr (Raw<T>::wide || K >= 8) {
+                rn_for_each_logit<T, K>(mine, [&](int, float x) { s += fast_ex2(fmaf(x, LOG2E, -off)); });
+            } else {
+#pragma unroll
+                for (int q = 0; q < K; ++q) s += fast_ex2(fmaf(rn_to_float<T>(mine[q]), LOG2E, -off));
+            }
+            s += __shfl_xor_sync(RN_FULL, s, 1);
+            s += __shfl_xor_sync(RN_FULL, s, 2);
+            lse_total += xmax + fast_lg2(s) * LN2;
+        }
+        if (u == 0) {
+#pragma unroll
+            for (int e = 0; e < K; ++e) {
+                beam_s[e] = digit_value<T>(dk[e]) + 0.0f;
+                beam_i[e] = digit_index(dk[e]);
+            }
+        } else {
+            float dv[K];
+            int dp[K];
+#pragma unroll
+            for (int e = 0; e < K; ++e) {
+                dv[e] = digit_value<T>(dk[e]);
+                dp[e] = digit_index(dk[e]) * stride;
+            }
+            Key64 blk[K];
+#pragma unroll
+            for (int e = 0; e < K; ++e) blk[e] = Key64{0u, 0u};
+            if (gl == 0) {          // row i = 0, already sorted
+#pragma unroll
+                for (int j = 0; j < K; ++j) blk[j] = Key64{rn_ord(beam_s[0] + dv[j] + 0.0f), ~uint32_t(beam_i[0] + dp[j])};
+            } else if (gl == 1) {   // column j = 0, i >= 1, already sorted
+#pragma unroll
+                for (int i = 1; i < K; ++i) blk[i - 1] = Key64{rn_ord(beam_s[i] + dv[0] + 0.0f), ~uint32_t(beam_i[i] + dp[0])};
+            } else if (gl == 2) {   // first block of the remainder
+                RemFill<K, 0, 1, 1>::run(blk, beam_s, beam_i, dv, dp);
+                oem_sort_desc<K>(blk);
+            } else if (NBLK > 1) {  // second block of the remainder
+                RemFill<K, 1, 1, 1>::run(blk, beam_s, beam_i, dv, dp);
+                oem_sort_desc<K>(blk);
+            }
+            fold_topk_xlane<K>(blk, 1);
+            fold_topk_xlane<K>(blk, 2);
+#pragma unroll
+            for (int e = 0; e < K; ++e) {
+                beam_s[e] = rn_unord(blk[e].hi);
+                beam_i[e] = int(~blk[e].lo);
+            }
+        }
+        stride *= P;
+    }
+
+    float logq[K];
+#pragma unroll
+    for (int e = 0; e < K; ++e) logq[e] = beam_s[e] - lse_total;
+    if (rho != 0.f && !inactive && logq[0] > -INFINITY) {
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < K; ++e) s += fast_ex2((logq[e] - logq[0]) * LOG2E);
+        const float l = logq[0] + fast_lg2(s) * LN2;
+#pragma unroll
+        for (int e = 0; e < K; ++e) logq[e] -= rho * l;
+    }
+#pragma unroll
+    for (int e = 0; e < K; ++e) {
+        const bool noop = inactive || logq[e] == -INFINITY;
+        content[e] = noop ? e : beam_i[e];
+        weight[e] = inactive ? 0.f : fast_ex2(logq[e] * LOG2E);
+    }
+}
+
 }  // namespace rn_fast

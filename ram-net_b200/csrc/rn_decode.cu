@@ -196,9 +196,10 @@ __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDe
 // ------------------------------------------------------------------------------------------
 // specialised decode step: 16 (b,h) pairs per CTA
 // ------------------------------------------------------------------------------------------
-// Warp 0 decodes the 32 addresses of the CTA (lanes 0-15 the write logits, 16-31 the read logits of
-// the 16 pairs) with the thread-per-row decoder, so the selection costs one warp-instruction per 32
-// addresses instead of one warp per address.  Then warp w owns pairs 2w and 2w+1: it loads the K
+// Warps 0-3 decode the 32 addresses of the CTA (16 pairs x write/read logits), four lanes per
+// address, with the register-resident sorting networks of rn_addr_fast.cuh: a warp instruction
+// serves 8 addresses and the dependent chain of one address is short enough to hide behind the
+// row traffic of the other resident CTA.  Then warp w owns pairs 2w and 2w+1: it loads the K
 // write rows of a pair at once (K 512-byte loads in flight), updates and stores them, then loads
 // the K read rows, reduces them in registers and applies the epilogue.  A lane always re-reads
 // exactly the 16 bytes of a row that it wrote itself, so no barrier separates writes from reads.
@@ -215,15 +216,17 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
     const int bh0 = blockIdx.x * RN_DECF_PAIRS;
     const int C = p.C;
 
-    if (warp == 0) {
-        const int pair = lane & 15, which = lane >> 4;
-        const int bh = bh0 + pair;
-        if (bh < BH) {
-            const int b = bh / p.H, h = bh % p.H;
-            const T *src = static_cast<const T *>(which ? p.r_addr : p.w_addr) + int64_t(bh) * U * P;
-            int content[K];
-            float weight[K];
-            rn_fast::thread_decode<T, U, P, K>(src, p.re_norm[which], content, weight);
+    if (warp < 4) {
+        // four lanes per address: 32 addresses (16 pairs x write/read) on warps 0-3
+        const int group = tid >> 2, gl = tid & 3;
+        const int pair = group & 15, which = group >> 4;
+        const int bh = min(bh0 + pair, BH - 1);  // surplus groups redo the last pair and discard it
+        const int b = bh / p.H, h = bh % p.H;
+        const T *src = static_cast<const T *>(which ? p.r_addr : p.w_addr) + int64_t(bh) * U * P;
+        int content[K];
+        float weight[K];
+        rn_fast::quad_decode<T, U, P, K>(src, p.re_norm[which], gl, content, weight);
+        if (gl == 0 && bh0 + pair < BH) {
             const int shift = (h < p.E) ? rn_pos_mod(p.pos[b], p.A) : 0;
 #pragma unroll
             for (int e = 0; e < K; ++e) {
