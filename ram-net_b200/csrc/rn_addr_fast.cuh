@@ -405,14 +405,16 @@ __device__ __forceinline__ void quad_decode(const T *src, const float rho, const
     bool inactive = false;
     int stride = 1;
 
-#pragma unroll
+    // the digit loop stays rolled: the straight-line networks are long and this code runs on few
+    // warps, so instruction fetch, not issue, would otherwise set the pace
+#pragma unroll 1
     for (int u = 0; u < U; ++u) {
         const T *mine = src + u * P + gl * K;  // this lane's K logits of digit u
         DKey dk[K];
         quad_make_keys<T, K>(mine, gl * K, dk);
         oem_sort_desc<K>(dk);
-        fold_topk_xlane<K>(dk, 1);
-        fold_topk_xlane<K>(dk, 2);
+#pragma unroll 1
+        for (int m = 1; m <= 2; m <<= 1) fold_topk_xlane<K>(dk, m);
         // dk[0..K) = the digit's K best logits, sorted, in all four lanes
         const float xmax = digit_value<T>(dk[0]);
         if (xmax == -INFINITY) {
@@ -455,13 +457,12 @@ __device__ __forceinline__ void quad_decode(const T *src, const float rho, const
                 for (int i = 1; i < K; ++i) blk[i - 1] = Key64{rn_ord(beam_s[i] + dv[0] + 0.0f), ~uint32_t(beam_i[i] + dp[0])};
             } else if (gl == 2) {   // first block of the remainder
                 RemFill<K, 0, 1, 1>::run(blk, beam_s, beam_i, dv, dp);
-                oem_sort_desc<K>(blk);
             } else if (NBLK > 1) {  // second block of the remainder
                 RemFill<K, 1, 1, 1>::run(blk, beam_s, beam_i, dv, dp);
-                oem_sort_desc<K>(blk);
             }
-            fold_topk_xlane<K>(blk, 1);
-            fold_topk_xlane<K>(blk, 2);
+            if (gl >= 2) oem_sort_desc<K>(blk);
+#pragma unroll 1
+            for (int m = 1; m <= 2; m <<= 1) fold_topk_xlane<K>(blk, m);
 #pragma unroll
             for (int e = 0; e < K; ++e) {
                 beam_s[e] = rn_unord(blk[e].hi);
