@@ -9,7 +9,8 @@
 // schedule kernel: EPT events per thread live in registers across all phases of a chunk
 // ------------------------------------------------------------------------------------------
 template <typename T, bool SMEM_TABLES, int EPT>
-__global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const RnGsuParams p) {
+__global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(const RnGsuParams p) {
+    const int NT = blockDim.x;  // threads of this CTA: EPT * NT >= events per chunk
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float gam[2][RN_GSU_LMAX];
     __shared__ int hist[RN_GSU_RMAX + 3];
@@ -41,7 +42,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
     if (bh == 0 && tid == 0) *p.status = 0;
 
     const float *mass_in = p.mass_in + int64_t(bh) * A;
-    for (int a = tid; a < A; a += RN_GSU_THREADS) {
+    for (int a = tid; a < A; a += NT) {
         if (SMEM_TABLES || mass_in != mass) mass[a] = mass_in[a];
         claim[a] = 0xffffffffu;
     }
@@ -50,7 +51,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
     int ev_t[EPT], ev_k[EPT];
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
-        const int e = j * RN_GSU_THREADS + tid;
+        const int e = j * NT + tid;
         ev_t[j] = e / KT;
         ev_k[j] = e - ev_t[j] * KT;
     }
@@ -113,12 +114,12 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
         for (;;) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
-                if (pend & (1u << j)) atomicMin(&claim[ea[j]], uint32_t(j * RN_GSU_THREADS + tid));
+                if (pend & (1u << j)) atomicMin(&claim[ea[j]], uint32_t(j * NT + tid));
             __syncthreads();
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
                 if (!(pend & (1u << j))) continue;
-                if (claim[ea[j]] == uint32_t(j * RN_GSU_THREADS + tid)) {
+                if (claim[ea[j]] == uint32_t(j * NT + tid)) {
                     if (ev_k[j] < p.Kw) {
                         em[j] = mass[ea[j]];
                         const RnGate g = rn_gate(ev[j], g_cur[ev_t[j]], em[j], p.eps);
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
         float *o_coef = reinterpret_cast<float *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 4);
         uint16_t *o_late = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
         uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 10);
-        for (int r = tid; r < R + 2; r += RN_GSU_THREADS) hist[r] = 0;
+        for (int r = tid; r < R + 2; r += NT) hist[r] = 0;
         __syncthreads();
         const int lane = tid & 31;
 #pragma unroll
@@ -193,7 +194,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
             reinterpret_cast<uint32_t *>(rec)[1] = uint32_t(acc);
         }
         __syncthreads();
-        for (int r = 1 + tid; r <= R; r += RN_GSU_THREADS) o_off[r] = uint16_t(hist[r]);
+        for (int r = 1 + tid; r <= R; r += NT) o_off[r] = uint16_t(hist[r]);
         __syncthreads();
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
@@ -212,7 +213,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
         // ---- the chunk record, in event order (coalesced) ------------------------------------------
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            const int e = j * RN_GSU_THREADS + tid;
+            const int e = j * NT + tid;
             if (e < NEp) {
                 const bool dead = er[j] < 0;
                 o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead);
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_schedule_kernel(const R
 
     if (SMEM_TABLES) {
         float *mass_out = p.mass_out + int64_t(bh) * A;
-        for (int a = tid; a < A; a += RN_GSU_THREADS) mass_out[a] = mass[a];
+        for (int a = tid; a < A; a += NT) mass_out[a] = mass[a];
     }
 }
 
@@ -591,6 +592,9 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     pl->NEp = int(rn_align(pl->NE, 8));
     int ept = (pl->NE + RN_GSU_THREADS - 1) / RN_GSU_THREADS;
     pl->ept = ept <= 1 ? 1 : (ept <= 2 ? 2 : (ept <= 4 ? 4 : (ept <= 8 ? 8 : 16)));
+    // schedule kernel: two events per thread (four when a chunk has more than 2048 events)
+    pl->sched_ept = pl->NE > 2 * RN_SCHED_THREADS_MAX ? 4 : 2;
+    pl->sched_threads = int(rn_align((pl->NE + pl->sched_ept - 1) / pl->sched_ept, 32));
     const size_t ev_bytes = size_t(pl->NE) * 8 + 16;  // mass-aware per-event scratch
     pl->smem_tables = (size_t(A) * 8 + ev_bytes) <= RN_SMEM_BUDGET;
     pl->sched_smem = rn_align((pl->smem_tables ? size_t(A) * 8 : 0) + ev_bytes, 16);
@@ -657,15 +661,15 @@ template <typename T, bool SMEM>
 static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int bh = p.B * p.H;
 #define RN_CASE(E)                                                                                              \
-    if (pl.ept == E) {                                                                                          \
+    if (pl.sched_ept == E) {                                                                                    \
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_schedule_kernel<T, SMEM, E>,                                        \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, int(pl.sched_smem)));         \
-        rn_gsu_schedule_kernel<T, SMEM, E><<<bh, RN_GSU_THREADS, pl.sched_smem, stream>>>(p);                   \
+        rn_gsu_schedule_kernel<T, SMEM, E><<<bh, pl.sched_threads, pl.sched_smem, stream>>>(p);                 \
         return 0;                                                                                               \
     }
-    RN_CASE(1) RN_CASE(2) RN_CASE(4) RN_CASE(8) RN_CASE(16)
+    RN_CASE(2) RN_CASE(4)
 #undef RN_CASE
-    rn_set_error("no schedule kernel for %d events per thread", pl.ept);
+    rn_set_error("no schedule kernel for %d events per thread", pl.sched_ept);
     return 1;
 }
 

@@ -32,7 +32,8 @@
 #include "rn_common.cuh"
 #include "rn_gsu.cuh"
 
-constexpr int RN_GSU_THREADS = 256;               // schedule kernel and generic apply kernel
+constexpr int RN_GSU_THREADS = 256;               // generic apply kernel, scalar backward kernel
+constexpr int RN_SCHED_THREADS_MAX = 1024;        // schedule kernel: 2 events per thread when possible
 constexpr int RN_GSU_LMAX = 64;                   // longest time chunk
 constexpr int RN_GSU_NE_MAX = 4096;               // most events per chunk (L * (Kw + Kr))
 constexpr int RN_GSU_RMAX = 2 * RN_GSU_LMAX;      // most rounds in a chunk
@@ -90,7 +91,8 @@ constexpr int RN_APPLY_THREADS = 1024;  // forward apply kernel
 constexpr int RN_SWEEP_THREADS = 512;   // backward replay / reverse kernels
 
 struct RnGsuPlan {
-    int L, nchunks, NE, NEp, ept;
+    int L, nchunks, NE, NEp, ept;  // ept: events per thread with RN_GSU_THREADS threads
+    int sched_threads, sched_ept;  // schedule kernel launch geometry
     int smem_tables;       // schedule kernel keeps mass + claim tables in shared memory
     size_t sched_smem;
     int wide;              // A > 65536: records carry a separate slot array
