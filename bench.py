@@ -346,8 +346,8 @@ def run_addr(args, device, rank, barrier, max_over_ranks):
 def cpu_baseline(reps=1):
     from oracle import ramnet_oracle as orc
     s = SHAPES["prefill"]
-    B, H, T = 1, 2, 256
-    U, P, K, C, E = s["U"], s["P"], s["K"], s["C"], 1
+    B, H, T = 1, 4, 2048
+    U, P, K, C, E = s["U"], s["P"], s["K"], s["C"], 2
     A = P ** U
     g = torch.Generator().manual_seed(0)
     w = torch.randn(B, T, H, U, P, generator=g).bfloat16().float().permute(0, 2, 3, 4, 1)
@@ -361,7 +361,7 @@ def cpu_baseline(reps=1):
         t0 = time.perf_counter()
         orc.ram_attn(w, r, x, gm, slot, mass, None, E, pos, (K, K))
         best = min(best, time.perf_counter() - t0)
-    # tokens carry all 16 heads in the metric; the sample ran H=2 of them
+    # tokens carry all 16 heads in the metric; the sample ran H=4 of them
     tokens = B * T * H / s["H"]
     return dict(value=tokens / best, unit="tokens/s", cores=torch.get_num_threads(), kind="port",
                 sample=f"oracle.ram_attn on B{B} H{H} T{T} U{U} P{P} K{K} C{C} fp32 (bf16-quantised inputs), "
@@ -418,7 +418,7 @@ def run_ncu_case(name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill"])

@@ -46,6 +46,19 @@ _lib.define(
     "gsu_backward(Tensor addr_idx, Tensor addr_val, Tensor x, Tensor gamma, Tensor init_slot, Tensor init_mass, "
     "Tensor? mask, Tensor D_y, Tensor D_post_slot, Tensor D_post_mass, int w_top_k, int r_top_k, bool mass_aware, "
     "float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)")
+# operators of the reference's event/segment formulation, kept for call compatibility: the slot of an
+# event is recovered from the segment tables and the work is done by the time-chunked kernels
+_lib.define(
+    "topk_segment_forward(Tensor addr_val, Tensor seg_idx, Tensor seg_off, Tensor seg_len, Tensor event_i, Tensor x, "
+    "Tensor gamma, Tensor init_slot, Tensor init_mass, int w_top_k, int r_top_k, bool mass_aware, float eps) "
+    "-> (Tensor, Tensor, Tensor, Tensor)")
+_lib.define(
+    "topk_segment_backward(Tensor seg_idx, Tensor seg_off, Tensor seg_len, Tensor event_i, Tensor event_v, Tensor x, "
+    "Tensor gamma, Tensor init_slot, Tensor init_mass, Tensor D_y, Tensor D_post_slot, Tensor D_post_mass, int w_top_k, "
+    "int r_top_k, bool mass_aware, float eps) -> (Tensor, Tensor, Tensor, Tensor, Tensor)")
+_lib.define(
+    "topk_segment_forward_(Tensor addr_val, Tensor seg_idx, Tensor seg_off, Tensor seg_len, Tensor event_i, Tensor x, "
+    "Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, int w_top_k, int r_top_k, bool mass_aware, float eps) -> Tensor")
 
 
 def _require_cuda(*tensors: torch.Tensor) -> None:
@@ -309,3 +322,69 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
                          ptr(d_x), strides(d_x), ptr(d_gamma), ptr(d_slot), ptr(d_mass), ptr(ws), int(nbytes), B, H, T, A,
                          C4, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
     return d_val, d_x[..., :C], d_gamma, d_slot[..., :C], d_mass
+
+
+# ----------------------------------------------------------------------------------------------
+# event / segment formulation (reference schemas, packages/ramnet-ops/csrc/ram_attn_bind.cpp:69-91)
+# ----------------------------------------------------------------------------------------------
+def _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, K, A):
+    """Rebuild (idx, val) of shape (B,H,K,T) from the grouped-event tables.
+
+    Events sit in ``event_i`` grouped by segment: positions [seg_off[s], seg_off[s] + seg_len[s]) belong to
+    slot ``seg_idx[s]``; positions covered by no segment are masked events (they become no-ops).  Event ids
+    flatten (b, h, t, k) with k fastest, which is exactly the token-major storage the kernels read.
+    Static shapes only, no host synchronisation."""
+    N = event_i.numel()
+    dev = event_i.device
+    pos = torch.arange(N, device=dev, dtype=torch.int64)
+    live_seg = seg_len > 0
+    starts = torch.where(live_seg, seg_off.to(torch.int64), torch.full_like(seg_off, N, dtype=torch.int64))
+    # tables indexed by sorted position: slot + 1 and end of the segment that starts there
+    slot_at = torch.zeros(N + 1, dtype=torch.int64, device=dev).scatter_(0, starts, seg_idx.to(torch.int64) + 1)
+    end_at = torch.zeros(N + 1, dtype=torch.int64, device=dev).scatter_(0, starts, (seg_off + seg_len).to(torch.int64))
+    start_of = torch.where(slot_at[:N] > 0, pos, torch.zeros_like(pos)).cummax(dim=0).values
+    slot = slot_at[start_of] - 1
+    covered = (slot >= 0) & (pos < end_at[start_of])
+    idx_flat = torch.zeros(N, dtype=torch.int32, device=dev)
+    val_flat = torch.zeros(N, dtype=torch.float32, device=dev)
+    where = event_i.to(torch.int64)
+    idx_flat.scatter_(0, where, torch.where(covered, slot, torch.zeros_like(slot)).to(torch.int32))
+    val_flat.scatter_(0, where, torch.where(covered, event_v.to(torch.float32), torch.zeros_like(val_flat)))
+    shape = (B, H, T, K)
+    return idx_flat.view(shape).permute(0, 1, 3, 2), val_flat.view(shape).permute(0, 1, 3, 2)
+
+
+def _event_values(addr_val, event_i):
+    return addr_val.transpose(-2, -1).reshape(-1).index_select(0, event_i.to(torch.int64))
+
+
+@torch.library.impl(_lib, "topk_segment_forward", "CUDA")
+def _topk_segment_forward(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k,
+                          mass_aware, eps):
+    B, H, T, C = x.shape
+    A = init_slot.shape[2]
+    event_v = _event_values(addr_val, event_i)
+    idx, val = _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, w_top_k + r_top_k, A)
+    y, slot, mass = _gsu_forward(idx, val, x, gamma, init_slot, init_mass, None, w_top_k, r_top_k, mass_aware, eps)
+    return y.to(torch.float32), slot, mass, event_v
+
+
+@torch.library.impl(_lib, "topk_segment_forward_", "CUDA")
+def _topk_segment_forward_(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, slot, mass, w_top_k, r_top_k,
+                           mass_aware, eps):
+    B, H, T, C = x.shape
+    event_v = _event_values(addr_val, event_i)
+    idx, val = _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, w_top_k + r_top_k, slot.shape[2])
+    y = gsu_forward_impl(idx, val, x, gamma, slot, mass, slot, mass, None, w_top_k, r_top_k, mass_aware, eps)
+    return y.to(torch.float32)
+
+
+@torch.library.impl(_lib, "topk_segment_backward", "CUDA")
+def _topk_segment_backward(seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, init_slot, init_mass, D_y, D_post_slot,
+                           D_post_mass, w_top_k, r_top_k, mass_aware, eps):
+    B, H, T, C = x.shape
+    idx, val = _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, w_top_k + r_top_k,
+                                      init_slot.shape[2])
+    d_val, d_x, d_gamma, d_slot, d_mass = _gsu_backward(idx, val, x, gamma, init_slot, init_mass, None, D_y.to(x.dtype),
+                                                        D_post_slot, D_post_mass, w_top_k, r_top_k, mass_aware, eps)
+    return d_val.contiguous(), d_x.to(torch.float32), d_gamma, d_slot, d_mass

@@ -155,3 +155,49 @@ def _gsu_backward(ctx, D_y, D_slot, D_mass):
 
 
 torch.library.register_autograd("ramnet_ops::gsu_forward", _gsu_backward, setup_context=_gsu_setup)
+
+
+# ---------------------------------------------------------------------------- event / segment schemas
+@torch.library.register_fake("ramnet_ops::topk_segment_forward")
+def _(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k, mass_aware, eps):
+    return (x.new_empty(x.shape, dtype=torch.float32), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
+            init_mass.new_empty(init_mass.shape, dtype=torch.float32), addr_val.new_empty(event_i.shape))
+
+
+@torch.library.register_fake("ramnet_ops::topk_segment_forward_")
+def _(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, slot, mass, w_top_k, r_top_k, mass_aware, eps):
+    return x.new_empty(x.shape, dtype=torch.float32)
+
+
+@torch.library.register_fake("ramnet_ops::topk_segment_backward")
+def _(seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, init_slot, init_mass, D_y, D_post_slot, D_post_mass,
+      w_top_k, r_top_k, mass_aware, eps):
+    B, H, T, _ = x.shape
+    return (x.new_empty((B, H, w_top_k + r_top_k, T), dtype=torch.float32), x.new_empty(x.shape, dtype=torch.float32),
+            gamma.new_empty(gamma.shape, dtype=torch.float32), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
+            init_mass.new_empty(init_mass.shape, dtype=torch.float32))
+
+
+def _segment_setup(ctx, inputs, output):
+    _, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k, mass_aware, eps = inputs
+    ctx.opts = (w_top_k, r_top_k, mass_aware, eps)
+    ctx.save_for_backward(seg_idx, seg_off, seg_len, event_i, output[3], x, gamma, init_slot, init_mass)
+    ctx.mark_non_differentiable(output[3])
+    ctx.set_materialize_grads(False)
+
+
+def _segment_backward(ctx, D_y, D_slot, D_mass, D_event_v):
+    seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, slot, mass = ctx.saved_tensors
+    w_top_k, r_top_k, mass_aware, eps = ctx.opts
+    d_addr, d_x, d_gamma, d_slot, d_mass = torch.ops.ramnet_ops.topk_segment_backward(
+        seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, slot, mass,
+        torch.zeros_like(x) if D_y is None else D_y,
+        torch.zeros_like(slot) if D_slot is None else D_slot, torch.zeros_like(mass) if D_mass is None else D_mass,
+        w_top_k, r_top_k, mass_aware, eps)
+    need = ctx.needs_input_grad
+    return (d_addr if need[0] else None,) + (None,) * 4 + (
+        d_x.to(x.dtype) if need[5] else None, d_gamma.to(gamma.dtype) if need[6] else None,
+        d_slot if need[7] else None, d_mass if need[8] else None) + (None,) * 4
+
+
+torch.library.register_autograd("ramnet_ops::topk_segment_forward", _segment_backward, setup_context=_segment_setup)

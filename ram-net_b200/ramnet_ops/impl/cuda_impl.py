@@ -11,11 +11,41 @@ this package's own kernels:
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
 import ramnet_ops._C  # noqa: F401  loads the C-ABI library and defines torch.ops.ramnet_ops.*
 from . import _cuda_autograd  # noqa: F401  fake kernels and autograd formulas
 from ._cuda_config import ADDRESS_LIMIT, check_int_capacity
+
+
+@dataclass(slots=True)
+class SegmentMeta:
+    """Grouped-event tables of the reference's segment formulation (fixed capacities: S = B*H*A segments,
+    N = B*H*T*(Kw+Kr) events).  This package's own path does not need them; they are provided so code written
+    against ``gather_segment`` + ``torch.ops.ramnet_ops.topk_segment_forward`` keeps working."""
+    seg_idx: torch.Tensor  # (S)
+    seg_off: torch.Tensor  # (S)
+    seg_len: torch.Tensor  # (S)
+    event_i: torch.Tensor  # (N)
+    event_v: torch.Tensor | None = None
+
+
+def gather_segment(addr_idx: torch.Tensor, mask: torch.Tensor | None, address_size: int) -> SegmentMeta:
+    """Group the events of ``addr_idx`` (B,H,Kw+Kr,T) by slot, time order kept inside a slot (same contract as
+    packages/ramnet-ops/src/ramnet_ops/impl/cuda_impl.py:72-102; no data-dependent shapes, no host sync)."""
+    B, H, K, T = addr_idx.shape
+    n_slots = B * H * address_size
+    keys = addr_idx.permute(0, 1, 3, 2).reshape(-1)  # event id = ((b*H + h)*T + t)*K + k
+    if mask is not None:
+        live = mask.to(torch.bool)[:, None, :, None].expand(B, H, T, K).reshape(-1)
+        keys = torch.where(live, keys, torch.full_like(keys, n_slots))  # masked events sort behind every slot
+    ordered, event_i = torch.sort(keys, stable=True)  # stable: time order, writes before reads of a token
+    edges = torch.searchsorted(ordered, torch.arange(n_slots + 1, device=keys.device, dtype=torch.int32), out_int32=True)
+    seg_len, order = torch.sort(edges[1:] - edges[:-1], descending=True)
+    seg_idx = torch.arange(n_slots, device=keys.device, dtype=torch.int32)[order]
+    return SegmentMeta(seg_idx, edges[:-1][order], seg_len, event_i.to(torch.int32))
 
 
 def _cuda_topk_autoregressive_(w_addr, r_addr, x, gamma, slot_, mass_, mask, embed_num, position_ids, w_top_k, r_top_k,

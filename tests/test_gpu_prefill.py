@@ -152,3 +152,35 @@ def test_prefill_equals_token_by_token_decode():
     assert_close_stats("y", torch.stack(ys, dim=2), full[0], **tol)
     assert_close_stats("slot", s.cpu(), full[1], **tol)
     assert_close_stats("mass", m.cpu(), full[2], **tol)
+
+
+def test_segment_formulation_ops_match_the_direct_path():
+    """gather_segment + torch.ops.ramnet_ops.topk_segment_forward[_] / backward (the reference's event
+    and segment schemas) give the results of the time-chunked operators."""
+    ops()
+    from ramnet_ops.impl.cuda_impl import gather_segment
+    B, H, U, P, T, C, K = 2, 3, 2, 8, 70, 12, (3, 5)
+    A = P ** U
+    w, r, x, g, slot, mass, mask, pos = make_case(B, H, U, P, T, C, torch.float32, 21, masked=True)
+    dev = "cuda"
+    idx, val = torch.ops.ramnet_ops.topk_addr_forward(w.to(dev), r.to(dev), 1, A, pos.to(dev).int(), K[0], K[1], 0.0, 0.5)
+    for m in (None, mask.to(dev)):
+        meta = gather_segment(idx, m, A)
+        assert meta.seg_idx.numel() == B * H * A and meta.event_i.numel() == B * H * T * sum(K)
+        xs, gs = x.to(dev).requires_grad_(True), g.to(dev)
+        s0, m0 = slot.to(dev).requires_grad_(True), mass.to(dev)
+        y, s1, m1, ev = torch.ops.ramnet_ops.topk_segment_forward(val, meta.seg_idx, meta.seg_off, meta.seg_len, meta.event_i,
+                                                                  xs, gs, s0, m0, K[0], K[1], False, 1e-6)
+        ry, rs, rm = torch.ops.ramnet_ops.gsu_forward(idx, val, x.to(dev), gs, slot.to(dev), m0, m, K[0], K[1], False, 1e-6)
+        assert y.dtype == torch.float32 and ev.shape == meta.event_i.shape
+        assert torch.equal(y, ry.float()) and torch.equal(s1, rs) and torch.equal(m1, rm)
+        gx, gs0 = torch.autograd.grad(y.sum() + s1.square().sum(), (xs, s0))
+        xs2, s02 = x.to(dev).requires_grad_(True), slot.to(dev).requires_grad_(True)
+        ry2, rs2, _ = torch.ops.ramnet_ops.gsu_forward(idx, val, xs2, gs, s02, m0, m, K[0], K[1], False, 1e-6)
+        hx, hs0 = torch.autograd.grad(ry2.sum() + rs2.square().sum(), (xs2, s02))
+        assert_close_stats("D_x", gx, hx, atol=1e-5, rtol=1e-5, max_err_rate=0.0)
+        assert_close_stats("D_slot", gs0, hs0, atol=1e-5, rtol=1e-5, max_err_rate=0.0)
+        s_in, m_in = slot.clone().to(dev), mass.clone().to(dev)
+        y2 = torch.ops.ramnet_ops.topk_segment_forward_(val, meta.seg_idx, meta.seg_off, meta.seg_len, meta.event_i,
+                                                        x.to(dev), gs, s_in, m_in, K[0], K[1], False, 1e-6)
+        assert torch.equal(y2, y) and torch.equal(s_in, s1) and torch.equal(m_in, m1)
