@@ -141,7 +141,7 @@ int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *idx_strides,
                int64_t Kr, int mass_aware, double eps, int device, void *stream);
 
 /*
- * Backward of the prefill update / read (non mass-aware reads).
+ * Backward of the prefill update / read (plain and mass-aware reads).
  * Replaces ramnet_ops::topk_segment_backward
  * (packages/ramnet-ops/csrc/ram_attn_ops.cpp:267-310, kernels
  *  packages/ramnet-ops/csrc/ram_attn_segment_parallel.cu:241-606).

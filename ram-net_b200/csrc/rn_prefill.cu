@@ -126,7 +126,8 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                         mass[ea[j]] = g.mass;
                         ec[j] = g.gain;
                     } else {
-                        ec[j] = p.mass_aware ? ev[j] * mass[ea[j]] : ev[j];
+                        em[j] = mass[ea[j]];
+                        ec[j] = p.mass_aware ? ev[j] * em[j] : ev[j];
                     }
                     er[j] = R;
                     claim[ea[j]] = 0xffffffffu;
@@ -226,6 +227,12 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
             for (int j = 0; j < EPT; ++j)
                 if (er[j] >= 0 && ev_k[j] < p.Kw)
                     p.prev_mass[(int64_t(bh) * p.T + t0 + ev_t[j]) * p.Kw + ev_k[j]] = em[j];
+        }
+        if (p.read_mass != nullptr) {
+#pragma unroll
+            for (int j = 0; j < EPT; ++j)
+                if (er[j] >= 0 && ev_k[j] >= p.Kw)
+                    p.read_mass[(int64_t(bh) * p.T + t0 + ev_t[j]) * p.Kr + (ev_k[j] - p.Kw)] = em[j];
         }
         __syncthreads();  // gam / tok_live of the next chunk are complete; ev_v / ev_c may be reused
     }

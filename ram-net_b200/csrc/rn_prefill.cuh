@@ -75,6 +75,7 @@ struct RnGsuParams {
     int wide;                 // records carry the separate u32 slot array
     uint32_t *claim;          // global claim table (B*H*A) when the tables do not fit shared memory
     float *prev_mass;         // optional: mass of the slot before each write, [(bh*T + t)*Kw + k] (backward)
+    float *read_mass;         // optional: mass of the slot at each read, [(bh*T + t)*Kr + k] (mass-aware backward)
     // apply kernel
     int cs;                   // channels per CTA (multiple of 4)
     int nslices;

@@ -253,20 +253,25 @@ __device__ __forceinline__ RnGateBwd rn_gate_bwd(float d_gain, float d_mass, flo
     return o;
 }
 
-template <typename T, bool SMEM_TABLE, int EPT>
+template <typename T, bool SMEM_TABLE, int EPT, bool MASS_AWARE>
 __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const RnGsuBwdParams bp) {
     const RnGsuParams &p = bp.f;
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float gam[RN_GSU_LMAX];
+    __shared__ float tok_scale[RN_GSU_LMAX], tok_dr[RN_GSU_LMAX], tok_du[RN_GSU_LMAX];
 
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
     const int tid = threadIdx.x;
-    const int A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, NEp = p.NEp;
+    const int A = p.A, Kw = p.Kw, Kr = p.Kr, KT = p.Kw + p.Kr, NEp = p.NEp;
     const bool pow2 = (A & (A - 1)) == 0;
 
+    // dynamic smem: [d_mass A] (SMEM_TABLE) | dg_term[L*Kw] | (mass-aware) rd_u, rd_r, rd_dot [L*Kr] each
     float *dmass = SMEM_TABLE ? reinterpret_cast<float *>(dyn) : bp.dmass_ws + int64_t(bh) * A;
-    float *dg_term = reinterpret_cast<float *>(dyn + (SMEM_TABLE ? size_t(A) * 4 : 0));  // [L * Kw]
+    float *dg_term = reinterpret_cast<float *>(dyn + (SMEM_TABLE ? size_t(A) * 4 : 0));
+    float *rd_u = dg_term + size_t(p.L) * Kw;
+    float *rd_r = rd_u + size_t(p.L) * Kr;
+    float *rd_dot = rd_r + size_t(p.L) * Kr;
     const float *src = bp.dmass_post + int64_t(bh) * A;
     for (int a = tid; a < A; a += RN_GSU_THREADS)
         if (SMEM_TABLE || src != dmass) dmass[a] = src[a];
@@ -290,8 +295,11 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
         const int R = int(*reinterpret_cast<const uint32_t *>(rec));
         if (tid < Lc) gam[tid] = rn_to_float<T>(gamma[(t0 + tid) * p.gt]);
         for (int i = tid; i < Lc * Kw; i += RN_GSU_THREADS) dg_term[i] = 0.f;
+        if (MASS_AWARE)
+            for (int i = tid; i < Lc * Kr; i += RN_GSU_THREADS) rd_u[i] = rd_r[i] = rd_dot[i] = 0.f;
+        __syncthreads();
 
-        // this thread's write events: round, slot, weight, mass before, d_gain
+        // this thread's live events: round, slot, weight, mass seen, d_gain (writes) / <slot, d_y> (reads)
         int er[EPT];
         uint32_t ea[EPT];
         float ew[EPT], em[EPT], eg[EPT];
@@ -301,7 +309,8 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
             ea[j] = 0;
             ew[j] = em[j] = eg[j] = 0.f;
             const int e = j * RN_GSU_THREADS + tid;
-            if (ev_t[j] < Lc && ev_k[j] < Kw && e < NEp) {
+            const bool is_write = ev_k[j] < Kw;
+            if (ev_t[j] < Lc && e < NEp && (is_write || MASS_AWARE)) {
                 const uint32_t meta = e_meta[ev_t[j] * KT + ev_k[j]];
                 if (!(meta & RN_EV_DEAD)) {
                     const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
@@ -309,21 +318,58 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
                     er[j] = rn_ev_round(meta);
                     ea[j] = pow2 ? uint32_t(raw & (A - 1)) : uint32_t(raw % A);
                     ew[j] = fabsf(p.val[o]);
-                    const int64_t wi = (int64_t(bh) * p.T + t0 + ev_t[j]) * Kw + ev_k[j];
-                    em[j] = p.prev_mass[wi];
-                    eg[j] = bp.dgain[wi];
+                    if (is_write) {
+                        const int64_t wi = (int64_t(bh) * p.T + t0 + ev_t[j]) * Kw + ev_k[j];
+                        em[j] = p.prev_mass[wi];
+                        eg[j] = bp.dgain[wi];
+                    } else {
+                        const int kr = ev_k[j] - Kw;
+                        em[j] = p.read_mass[(int64_t(bh) * p.T + t0 + ev_t[j]) * Kr + kr];
+                        eg[j] = bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt];
+                        rd_u[ev_t[j] * Kr + kr] = ew[j] * em[j];
+                        rd_r[ev_t[j] * Kr + kr] = ew[j];
+                        rd_dot[ev_t[j] * Kr + kr] = eg[j];
+                    }
                 }
             }
         }
         __syncthreads();
+        if (MASS_AWARE) {
+            // y = scale * sum_k u_k slot_k,  u = r m,  scale = sum r / (sum u + eps)
+            if (tid < Lc) {
+                float U = 0.f, Rs = 0.f, ds = 0.f;
+                for (int k = 0; k < Kr; ++k) {
+                    U += rd_u[tid * Kr + k];
+                    Rs += rd_r[tid * Kr + k];
+                    ds += rd_u[tid * Kr + k] * rd_dot[tid * Kr + k];  // d(loss)/d(scale) = <d_y, sum_k u_k slot_k>
+                }
+                const float inv = 1.f / (U + p.eps);
+                tok_scale[tid] = Rs * inv;
+                tok_dr[tid] = ds * inv;                 // d(loss)/d(sum r)
+                tok_du[tid] = -ds * Rs * inv * inv;     // d(loss)/d(sum u)
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                if (er[j] < 0 || ev_k[j] < Kw) continue;
+                const float d_u = tok_scale[ev_t[j]] * eg[j] + tok_du[ev_t[j]];
+                bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt] =
+                    d_u * em[j] + tok_dr[ev_t[j]];
+                eg[j] = d_u * ew[j];  // flows into the mass the read saw
+            }
+        }
         for (int r = R - 1; r >= 0; --r) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
                 if (er[j] != r) continue;
-                const RnGateBwd g = rn_gate_bwd(eg[j], dmass[ea[j]], ew[j], gam[ev_t[j]], em[j], p.eps);
-                dmass[ea[j]] = g.d_prev_mass;
-                dg_term[ev_t[j] * Kw + ev_k[j]] = g.d_gamma;
-                bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt] = g.d_w;
+                if (ev_k[j] < Kw) {
+                    const RnGateBwd g = rn_gate_bwd(eg[j], dmass[ea[j]], ew[j], gam[ev_t[j]], em[j], p.eps);
+                    dmass[ea[j]] = g.d_prev_mass;
+                    dg_term[ev_t[j] * Kw + ev_k[j]] = g.d_gamma;
+                    bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt] = g.d_w;
+                } else {
+                    dmass[ea[j]] += eg[j];
+                }
             }
             __syncthreads();
         }
@@ -344,15 +390,18 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
 // host side
 // ------------------------------------------------------------------------------------------
 struct RnBwdLayout {
-    size_t off_fwd, off_prev_mass, off_dgain, off_delta, total;
+    size_t off_fwd, off_prev_mass, off_read_mass, off_dgain, off_delta, total;
 };
 
-static void rn_bwd_layout(const RnGsuPlan &pl, int64_t B, int64_t H, int64_t T, int64_t C, int64_t Kw, RnBwdLayout *lo) {
+static void rn_bwd_layout(const RnGsuPlan &pl, int64_t B, int64_t H, int64_t T, int64_t C, int64_t Kw, int64_t Kr,
+                          RnBwdLayout *lo) {
     size_t off = 0;
     lo->off_fwd = off;
     off = rn_align(off + pl.total, 256);
     lo->off_prev_mass = off;
     off = rn_align(off + size_t(B * H * T * Kw) * 4, 256);
+    lo->off_read_mass = off;
+    off = rn_align(off + size_t(B * H * T * Kr) * 4, 256);
     lo->off_dgain = off;
     off = rn_align(off + size_t(B * H * T * Kw) * 4, 256);
     lo->off_delta = off;
@@ -366,7 +415,7 @@ extern "C" int64_t rn_gsu_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, i
     RnGsuPlan pl;
     if (rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return -1;
     RnBwdLayout lo;
-    rn_bwd_layout(pl, B, H, T, C, Kw, &lo);
+    rn_bwd_layout(pl, B, H, T, C, Kw, Kr, &lo);
     return int64_t(lo.total);
 }
 
@@ -388,14 +437,14 @@ static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaSt
     return 1;
 }
 
-template <typename T, bool SMEM>
+template <typename T, bool SMEM, bool MA>
 static int rn_launch_scalar_bwd(const RnGsuBwdParams &bp, const RnGsuPlan &pl, size_t smem, cudaStream_t stream) {
     const int bh = bp.f.B * bp.f.H;
 #define RN_CASE(E)                                                                                                   \
     if (pl.ept == E) {                                                                                               \
-        RN_CUDA(cudaFuncSetAttribute(rn_gsu_scalar_bwd_kernel<T, SMEM, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                     int(smem)));                                                                    \
-        rn_gsu_scalar_bwd_kernel<T, SMEM, E><<<bh, RN_GSU_THREADS, smem, stream>>>(bp);                              \
+        RN_CUDA(cudaFuncSetAttribute(rn_gsu_scalar_bwd_kernel<T, SMEM, E, MA>,                                       \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));                       \
+        rn_gsu_scalar_bwd_kernel<T, SMEM, E, MA><<<bh, RN_GSU_THREADS, smem, stream>>>(bp);                          \
         return 0;                                                                                                    \
     }
     RN_CASE(1) RN_CASE(2) RN_CASE(4) RN_CASE(8) RN_CASE(16)
@@ -417,11 +466,17 @@ static int rn_run_bwd(const RnGsuBwdParams &bp, const RnGsuPlan &pl, int dtype, 
     if (int rc = rn_launch_sweep<T, true>(bp, pl, stream)) return rc;
     RN_CUDA(cudaGetLastError());
     rn_prof_mark(stream);
-    const bool smem_table = size_t(bp.f.A) * 4 + size_t(pl.L) * bp.f.Kw * 4 <= 200 * 1024;
-    const size_t smem = (smem_table ? size_t(bp.f.A) * 4 : 0) + size_t(pl.L) * bp.f.Kw * 4;
-    if (int rc = smem_table ? rn_launch_scalar_bwd<T, true>(bp, pl, smem, stream)
-                            : rn_launch_scalar_bwd<T, false>(bp, pl, smem, stream))
-        return rc;
+    const size_t ev_smem = size_t(pl.L) * (bp.f.Kw + 3 * bp.f.Kr) * 4;
+    const bool smem_table = size_t(bp.f.A) * 4 + ev_smem <= 200 * 1024;
+    const size_t smem = (smem_table ? size_t(bp.f.A) * 4 : 0) + ev_smem;
+    int rc;
+    if (bp.f.mass_aware)
+        rc = smem_table ? rn_launch_scalar_bwd<T, true, true>(bp, pl, smem, stream)
+                        : rn_launch_scalar_bwd<T, false, true>(bp, pl, smem, stream);
+    else
+        rc = smem_table ? rn_launch_scalar_bwd<T, true, false>(bp, pl, smem, stream)
+                        : rn_launch_scalar_bwd<T, false, false>(bp, pl, smem, stream);
+    if (rc) return rc;
     RN_CUDA(cudaGetLastError());
     rn_prof_mark(stream);
     return 0;
@@ -441,7 +496,6 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
                    d_slot && d_mass && workspace,
                "null pointer argument");
     RN_REQUIRE(dtype == RN_F32 || dtype == RN_F16 || dtype == RN_BF16, "unsupported dtype code %d", dtype);
-    RN_REQUIRE(!mass_aware, "the backward pass of mass_aware reads is not implemented");
     RN_REQUIRE(x_strides[3] == 1 && dy_strides[3] == 1 && dx_strides[3] == 1, "Tensor x / d_y / d_x last dim must be contiguous");
     RnGsuPlan pl;
     if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return rc;
@@ -454,7 +508,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
                      dx_strides[0] | dx_strides[1] | dx_strides[2]) & 3) == 0,
                "x, d_y and d_x must be aligned to 4 elements (pointer and strides)");
     RnBwdLayout lo;
-    rn_bwd_layout(pl, B, H, T, C, Kw, &lo);
+    rn_bwd_layout(pl, B, H, T, C, Kw, Kr, &lo);
     RN_REQUIRE(workspace_bytes >= int64_t(lo.total), "workspace too small: %lld < %lld bytes", (long long)workspace_bytes,
                (long long)lo.total);
     RN_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
@@ -474,7 +528,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     p.slot_in = slot_in; p.mass_in = mass_in;
     p.B = int(B); p.H = int(H); p.T = int(T); p.A = int(A); p.C = int(C); p.Kw = int(Kw); p.Kr = int(Kr);
     p.L = pl.L; p.nchunks = pl.nchunks; p.NE = pl.NE; p.NEp = pl.NEp;
-    p.mass_aware = 0; p.eps = float(eps);
+    p.mass_aware = mass_aware; p.eps = float(eps);
     unsigned char *fws = ws + lo.off_fwd;
     p.status = reinterpret_cast<int *>(fws);
     p.records = fws + pl.off_records;
@@ -483,6 +537,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     p.claim = reinterpret_cast<uint32_t *>(fws + pl.off_claim);
     p.cs = pl.cs; p.nslices = pl.nslices; p.state_in_smem = pl.state_in_smem;
     p.prev_mass = reinterpret_cast<float *>(ws + lo.off_prev_mass);
+    p.read_mass = mass_aware ? reinterpret_cast<float *>(ws + lo.off_read_mass) : nullptr;
     // the schedule kernel writes the final mass somewhere: d_mass doubles as that scratch before
     // the scalar kernel overwrites it with the gradient
     p.mass_out = d_mass;
