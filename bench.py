@@ -254,6 +254,10 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
         return sum(v) / max(len(v), 1)
 
     per_bh = T * (C * 2 + C * 2) + 2 * A * C * 4  # apply kernel: x once, y once, slot state in and out
+    # DRAM traffic of the apply kernel from the ncu capture of the small case (B2 T4096 H16: 143.9 MB read
+    # + 68.3 MB written, profiles/rn_gsu_apply_fast_kernel_prefill_small.md), per (b,t,h); it grows in
+    # proportion to the units processed (event records and x/y rows per token-head)
+    traffic = (143.941888e6 + 68.328704e6) / (2 * 4096 * 16) * (B * T * H)
     step_bytes = B * H * (T * (2 * U * P * 2 + C * 2 + 2 + C * 2) + 2 * A * C * 4 + 2 * A * 4)
     return dict(
         tokens_per_step=B * T, ms_total=ms, steps=args.steps, e2e_ms_total=e2e_ms, e2e_steps=e2e_steps,
@@ -261,6 +265,7 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
         kernels={"rn_addr_fast_kernel": mean(t_addr), "rn_gsu_schedule_kernel": mean(t_sched),
                  "rn_gsu_apply_fast_kernel": mean(t_apply)},
         dominant=("rn_gsu_apply_fast_kernel", B * H * per_bh, mean(t_apply)), step_bytes=step_bytes, bwd=bwd,
+        traffic=traffic,
         workload="prefill_fwd B8 T16384 H16 U2 P64(A4096) Kw16 Kr16 C128 bf16, CAPE on 8 heads, zero fp32 state")
 
 
@@ -346,7 +351,7 @@ def run_addr(args, device, rank, barrier, max_over_ranks):
 def cpu_baseline(reps=1):
     from oracle import ramnet_oracle as orc
     s = SHAPES["prefill"]
-    B, H, T = 1, 4, 2048
+    B, H, T = 1, 4, 4096
     U, P, K, C, E = s["U"], s["P"], s["K"], s["C"], 2
     A = P ** U
     g = torch.Generator().manual_seed(0)
@@ -502,7 +507,7 @@ def main():
         "gpu_launches": m["launches_per_step"] * args.steps,
         "clocks": m["clocks"],
         "roofline": {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": m["traffic"],
                      "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kms},
         "roofline_step": {"algorithmic_bytes": m["step_bytes"], "achieved": m["step_bytes"] / (ms_per_step / 1e3) / 1e9,
                           "frac": m["step_bytes"] / (ms_per_step / 1e3) / 1e9 / peak},
