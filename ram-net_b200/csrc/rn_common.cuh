@@ -84,6 +84,25 @@ template <> __device__ __forceinline__ float4 rn_load4<__nv_bfloat16>(const __nv
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
     return make_float4(a.x, a.y, b.x, b.y);
 }
+// Four elements as loaded, not yet converted: a prefetch keeps these so that the conversion (the first use
+// of the loaded registers) happens when the value is needed, not right behind the load.
+template <typename T> struct RnRaw4 { uint2 v; };
+template <> struct RnRaw4<float> { float4 v; };
+template <typename T> __device__ __forceinline__ RnRaw4<T> rn_zero_raw4() { RnRaw4<T> r; r.v = make_uint2(0u, 0u); return r; }
+template <> __device__ __forceinline__ RnRaw4<float> rn_zero_raw4<float>() { RnRaw4<float> r; r.v = make_float4(0.f, 0.f, 0.f, 0.f); return r; }
+template <typename T> __device__ __forceinline__ RnRaw4<T> rn_load_raw4(const T *p) { RnRaw4<T> r; r.v = *reinterpret_cast<const uint2 *>(p); return r; }
+template <> __device__ __forceinline__ RnRaw4<float> rn_load_raw4<float>(const float *p) { RnRaw4<float> r; r.v = *reinterpret_cast<const float4 *>(p); return r; }
+__device__ __forceinline__ float4 rn_cvt_raw4(const RnRaw4<float> &r) { return r.v; }
+__device__ __forceinline__ float4 rn_cvt_raw4(const RnRaw4<__half> &r) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.v.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 rn_cvt_raw4(const RnRaw4<__nv_bfloat16> &r) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
 template <typename T> __device__ __forceinline__ void rn_store4(T *p, float4 v);
 template <> __device__ __forceinline__ void rn_store4<float>(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
 template <> __device__ __forceinline__ void rn_store4<__half>(__half *p, float4 v) {

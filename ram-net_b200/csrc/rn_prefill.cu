@@ -13,9 +13,9 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     const int NT = blockDim.x;  // threads of this CTA: EPT * NT >= events per chunk
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float gam[2][RN_GSU_LMAX];
-    __shared__ int hist[RN_GSU_RMAX + 3];
     __shared__ float tok_scale[RN_GSU_LMAX];
     __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
+    __shared__ int n_heads[4];  // chains with >= 3, 2, 1 events after the first; then the running offsets
 
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
@@ -23,15 +23,23 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     const int A = p.A, KT = p.Kw + p.Kr, NEp = p.NEp;
     const bool pow2 = (A & (A - 1)) == 0;
 
-    // dynamic smem: [mass A][claim A] (SMEM_TABLES) | ev_v[NE] ev_c[NE] (mass-aware only)
+    // dynamic smem: [mass A][claim A][nxt NEp][last A][clen A] (SMEM_TABLES) | ev_v[NE] ev_c[NE] (mass-aware only)
     unsigned char *cur = dyn;
     float *mass;
     uint32_t *claim;
+    // successor of every event on its slot; latest event of every slot; events after the first on a slot
+    uint16_t *nxt = nullptr, *last = nullptr, *clen = nullptr;
     if (SMEM_TABLES) {
         mass = reinterpret_cast<float *>(cur);
         cur += size_t(A) * 4;
         claim = reinterpret_cast<uint32_t *>(cur);
         cur += size_t(A) * 4;
+        nxt = reinterpret_cast<uint16_t *>(cur);
+        cur += size_t(NEp) * 2;
+        last = reinterpret_cast<uint16_t *>(cur);
+        cur += (size_t(A) * 2 + 15) / 16 * 16;
+        clen = reinterpret_cast<uint16_t *>(cur);
+        cur += (size_t(A) * 2 + 15) / 16 * 16;
     } else {
         mass = p.mass_out + int64_t(bh) * A;
         claim = p.claim + int64_t(bh) * A;
@@ -94,6 +102,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         float ev[EPT], ec[EPT], em[EPT];  // slot, weight, coefficient, mass before the write
         int er[EPT];          // round, or -1 dead (zero weight / masked token), -3 out of range
         uint32_t pend = 0;
+        if (tid < 4) n_heads[tid] = 0;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             er[j] = -3;
@@ -106,6 +115,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 er[j] = live ? 0 : -1;
                 if (live) pend |= 1u << j;
             }
+            if (SMEM_TABLES && j * NT + tid < NEp) nxt[j * NT + tid] = 0xffffu;
         }
         prefetch(chunk + 1);
 
@@ -128,6 +138,11 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                     } else {
                         em[j] = mass[ea[j]];
                         ec[j] = p.mass_aware ? ev[j] * em[j] : ev[j];
+                    }
+                    if (SMEM_TABLES) {  // link the slot's events in time order (one winner per slot and round)
+                        if (R > 0) nxt[last[ea[j]]] = uint16_t(j * NT + tid);
+                        last[ea[j]] = uint16_t(j * NT + tid);
+                        if (R > 0) clen[ea[j]] = uint16_t(R);  // ends as the length of the slot's chain
                     }
                     er[j] = R;
                     claim[ea[j]] = 0xffffffffu;
@@ -163,55 +178,54 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 if (ev_t[j] < Lc && ev_k[j] >= p.Kw && er[j] >= 0) ec[j] *= tok_scale[ev_t[j]];
         }
 
-        // ---- events of round >= 1, counting-sorted by round (warp-aggregated atomics) ------------
+        // ---- the chunk record, in event order (coalesced) ------------------------------------------
         unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
-        uint16_t *o_off = reinterpret_cast<uint16_t *>(rec + 8);  // o_off[r], r = 1 .. R
         uint32_t *o_meta = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES);
         float *o_coef = reinterpret_cast<float *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 4);
-        uint16_t *o_late = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
-        uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 10);
-        for (int r = tid; r < R + 2; r += NT) hist[r] = 0;
-        __syncthreads();
-        const int lane = tid & 31;
+        uint2 *o_pair = reinterpret_cast<uint2 *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 8);
+        uint16_t *o_heads = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 16);
+        uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 17 + 16);
+        if (tid == 0) reinterpret_cast<uint32_t *>(rec)[0] = uint32_t(R);
+        // chain heads (round-1 events), the longest chains first so that the threads of a warp of the apply
+        // kernel walk chains of equal length: three classes, warp-aggregated counting then placement
+        int hcls[EPT];
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            const bool emit = er[j] >= 1;
-            const unsigned act = __ballot_sync(RN_FULL, emit);
-            if (emit) {
-                const unsigned grp = __match_any_sync(act, er[j]);
-                if (lane == __ffs(grp) - 1) atomicAdd(&hist[er[j] + 1], __popc(grp));
+            hcls[j] = -1;
+            if (er[j] == 1) {
+                const int len = SMEM_TABLES ? int(clen[ea[j]]) : 1;
+                hcls[j] = len >= 3 ? 0 : (len == 2 ? 1 : 2);
+            }
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const unsigned act = __ballot_sync(RN_FULL, hcls[j] == c);
+                if (act != 0u && (tid & 31) == __ffs(act) - 1) atomicAdd(&n_heads[c], __popc(act));
             }
         }
         __syncthreads();
         if (tid == 0) {
-            int acc = 0;
-            for (int r = 1; r <= R; ++r) {   // hist[r + 1] holds the count of round r
-                const int cnt = hist[r + 1];
-                hist[r] = acc;               // first entry of round r
-                acc += cnt;
-            }
-            hist[R] = acc;                   // rounds run 0 .. R-1: hist[R] = n_late
-            reinterpret_cast<uint32_t *>(rec)[0] = uint32_t(R);
-            reinterpret_cast<uint32_t *>(rec)[1] = uint32_t(acc);
+            const int n0 = n_heads[0], n1 = n_heads[1], n2 = n_heads[2];
+            n_heads[0] = 0;
+            n_heads[1] = n0;
+            n_heads[2] = n0 + n1;
+            o_heads[0] = uint16_t(n0 + n1 + n2);
         }
-        __syncthreads();
-        for (int r = 1 + tid; r <= R; r += NT) o_off[r] = uint16_t(hist[r]);
         __syncthreads();
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            const bool emit = er[j] >= 1;
-            const unsigned act = __ballot_sync(RN_FULL, emit);
-            if (emit) {
-                const unsigned grp = __match_any_sync(act, er[j]);
-                const int leader = __ffs(grp) - 1;
-                int base = 0;
-                if (lane == leader) base = atomicAdd(&hist[er[j]], __popc(grp));
-                base = __shfl_sync(grp, base, leader);
-                o_late[base + __popc(grp & ((1u << lane) - 1u))] = uint16_t(ev_t[j] | (ev_k[j] << 6));
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const bool emit = hcls[j] == c;
+                const unsigned act = __ballot_sync(RN_FULL, emit);
+                if (act != 0u) {
+                    const int lane = tid & 31, leader = __ffs(act) - 1;
+                    int base = 0;
+                    if (lane == leader) base = atomicAdd(&n_heads[c], __popc(act));
+                    base = __shfl_sync(RN_FULL, base, leader);
+                    if (emit) o_heads[8 + base + __popc(act & ((1u << lane) - 1u))] = uint16_t(j * NT + tid);
+                }
             }
         }
-
-        // ---- the chunk record, in event order (coalesced) ------------------------------------------
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             const int e = j * NT + tid;
@@ -219,6 +233,14 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 const bool dead = er[j] < 0;
                 o_meta[e] = rn_ev_pack(ea[j], dead ? 0 : er[j], dead);
                 o_coef[e] = dead ? 0.f : ec[j];
+                uint32_t link = RN_LINK_DEAD;
+                if (!dead) {
+                    const uint32_t kind = er[j] == 0 ? RN_KIND_FIRST : (er[j] == 1 ? RN_KIND_HEAD : RN_KIND_LATER);
+                    link = (ea[j] & 0xffffu) | (kind << RN_LINK_KIND_SHIFT);
+                    const uint32_t nx = SMEM_TABLES ? nxt[e] : 0xffffu;
+                    if (nx != 0xffffu) link |= RN_LINK_NEXT | (nx << 16);
+                }
+                o_pair[e] = make_uint2(__float_as_uint(dead ? 0.f : ec[j]), link);
                 if (p.wide) o_slot[e] = ea[j];
             }
         }
@@ -292,7 +314,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
         const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
         const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
         const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 10);
+        const uint32_t *e_slot = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 17 + 16);
         const int R = int(*reinterpret_cast<const uint32_t *>(rec));
 
         for (int i = tid; i < Lc * cs; i += RN_GSU_THREADS) {
@@ -371,13 +393,16 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
 // ------------------------------------------------------------------------------------------
 // fast apply kernel: C % 4 == 0, A <= 65536; slice state + streamed chunk records in shared memory.
 //
-// Round 0 (the first live event of every slot in the chunk, ~80 % of the events) is applied
-// token-major: the CTA's threads are split into one group per token; thread (q, sub) of a group
-// owns the events k = q, q + KL, ... of that token for the 4 channels sub*4 .. sub*4+3, with x[t] in
-// registers (prefetched one chunk ahead) and the token's output accumulating in registers.  The
-// later rounds are sparse; they are applied from the round-sorted late[] list, one (event, channel
-// group) per thread, so the lanes stay dense; their reads go through a per-(token,k) buffer that
-// the token's owners add in a fixed order afterwards.  One CTA barrier per round.
+// The first event of every slot in a chunk (~80 % of the events) is applied token-major: the CTA's
+// threads are split into one group per token; thread (q, sub) of a group owns the events k = q,
+// q + KL, ... of that token for the 4 channels sub*4 .. sub*4+3, with x[t] in registers and the
+// token's output accumulating in registers.  First events touch pairwise different slots, so a
+// thread requests the records and then the rows of all its events before it uses any of them.
+// The later events of a slot form a chain (link words of the record); the chains of a chunk are
+// dealt evenly to the thread groups from the record's head list, a group walks its chain with the
+// row in registers, and the reads of a chain go through a per-(token,k) buffer to the token's
+// owners.  Two CTA barriers per chunk; the records are double buffered by 1-D bulk copies and only
+// one thread polls the copy's mbarrier.
 // ------------------------------------------------------------------------------------------
 template <typename T, int CS, int EV>
 __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2) {
@@ -392,7 +417,8 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     const int C = p.C, A = p.A, Kw = p.Kw, Kr = p.Kr, KT = p.Kw + p.Kr, L = p.L;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);  // multiple of 4
-    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 10);  // header, meta, coef, late
+    const uint32_t rec_copy = uint32_t(size_t(p.NEp) * 9 + 16);  // {coef, link}[NEp], heads[8 + NEp/2]
+    const uint32_t kt_magic = 0xffffffffu / uint32_t(KT) + 1u;  // e / KT == __umulhi(e, kt_magic) for e < 4096
 
     // thread -> (token of the chunk, k-lane, channel group)
     const int TPT = 1 << tpt_log2;          // threads per token (8, 16 or 32: a group never leaves its warp)
@@ -415,11 +441,18 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
         rn_mbar_fence_init();
     }
     __syncthreads();
-    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes;
-    if (tid == 0) {
-        rn_mbar_expect_tx(&mbar[0], rec_copy);
-        rn_bulk_g2s(rec0, records, rec_copy, &mbar[0]);
-    }
+    // the part of a chunk record this kernel reads: the {coef, link} pairs and the head list, contiguous
+    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8;
+    auto fetch = [&](int chunk) {  // one thread; the target buffer was last read before a CTA barrier
+        uint64_t *bar = &mbar[chunk & 1];
+        rn_mbar_expect_tx(bar, rec_copy);
+        rn_bulk_g2s(rec0 + (chunk & 1) * rec_stride, records + int64_t(chunk) * p.rec_bytes, rec_copy, bar);
+    };
+    auto landed = [&](int chunk) {  // one thread: bounded wait for the copy of a chunk's record
+        return rn_mbar_wait_bounded(&mbar[chunk & 1], uint32_t(chunk >> 1) & 1u);
+    };
+    bool failed = false;
+    if (tid == 0) fetch(0);
 
     // state slice -> shared memory
     {
@@ -434,107 +467,121 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     const T *x = static_cast<const T *>(p.x) + b * p.xb + h * p.xh + c0 + sub * 4;
     T *y = static_cast<T *>(p.y) + b * p.yb + h * p.yh + c0 + sub * 4;
 
-    auto load_x = [&](int chunk) {
+    auto load_x = [&](int chunk) {  // raw bits: converted one chunk later, when the load has long landed
         const int t = chunk * L + tok;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (chunk < p.nchunks && tok < L && t < p.T && chan_ok) v = rn_load4<T>(x + int64_t(t) * p.xt);
+        RnRaw4<T> v = rn_zero_raw4<T>();
+        if (chunk < p.nchunks && tok < L && t < p.T && chan_ok) v = rn_load_raw4<T>(x + int64_t(t) * p.xt);
         return v;
     };
-    float4 xnext = load_x(0);
-    __syncthreads();
 
-    bool failed = false;
+    RnRaw4<T> xnext = load_x(0);
+    if (tid == 0 && !landed(0)) failed = true;
+    if (__syncthreads_or(failed)) {  // state and barriers are set up, the first record has landed
+        if (tid == 0) atomicExch(p.status, 1);
+        return;
+    }
+
     for (int chunk = 0; chunk < p.nchunks; ++chunk) {
-        const int buf = chunk & 1;
         const int t0 = chunk * L;
-        const int Lc = min(L, p.T - t0);
-        const bool more = chunk + 1 < p.nchunks;
-        const float4 xv = xnext;
-        // prefetch the next chunk: its record by bulk copy, its x row into registers
-        if (more && tid == 0) {
-            rn_fence_proxy_async();
-            rn_mbar_expect_tx(&mbar[buf ^ 1], rec_copy);
-            rn_bulk_g2s(rec0 + (buf ^ 1) * rec_stride, records + int64_t(chunk + 1) * p.rec_bytes, rec_copy,
-                        &mbar[buf ^ 1]);
-        }
+        const bool tok_ok = tok < min(L, p.T - t0);
+        const bool has_next = chunk + 1 < p.nchunks;
+        const float4 xv = rn_cvt_raw4(xnext);
+        if (tid == 0 && has_next) fetch(chunk + 1);
         xnext = load_x(chunk + 1);
-        if (!rn_mbar_wait_bounded(&mbar[buf], (chunk >> 1) & 1)) failed = true;
-        if (__syncthreads_or(failed)) {
-            // a bulk copy never completed: record it, give the copy in flight a last bounded chance
-            // to land (it targets this CTA's shared memory), and leave
-            if (tid == 0) atomicExch(p.status, 1);
-            if (more) rn_mbar_wait_bounded(&mbar[buf ^ 1], ((chunk + 1) >> 1) & 1);
-            return;
-        }
+        const unsigned char *rec = rec0 + (chunk & 1) * rec_stride;
+        const uint2 *e_pair = reinterpret_cast<const uint2 *>(rec);
+        const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(p.NEp) * 8);
 
-        const unsigned char *rec = rec0 + buf * rec_stride;
-        const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
-        const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const uint16_t *e_late = reinterpret_cast<const uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
-        const uint16_t *late_off = reinterpret_cast<const uint16_t *>(rec + 8);
-        const int R = int(reinterpret_cast<const uint32_t *>(rec)[0]);
-
-        // ---- round 0, token-major ----------------------------------------------------------------------
-        const bool tok_ok = tok < Lc;
+        // ---- first events, token-major: records, then rows, then arithmetic, then stores ------------------
         if (q == 0 && tok < L) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        uint32_t late = 0;  // this thread's reads of later rounds, added after those rounds
+        uint32_t late = 0;  // this thread's reads that a chain delivers
+        constexpr int NB = EV < 2 ? EV : 2;  // events in flight per thread
 #pragma unroll
-        for (int j = 0; j < EV; ++j) {
-            const int k = q + j * KL;
-            if (!tok_ok || k >= KT) continue;
-            const uint32_t m = e_meta[tok * KT + k];
-            if (m & (RN_EV_DEAD | 0x00ff0000u)) {  // dead, or a later round
-                if (!(m & RN_EV_DEAD) && k >= Kw) late |= 1u << j;
-                continue;
+        for (int jb = 0; jb < EV; jb += NB) {
+            uint2 pr[NB];
+            float4 row[NB];
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                const int k = q + (jb + i) * KL;
+                pr[i] = make_uint2(0u, RN_LINK_DEAD);
+                if (tok_ok && k < KT) pr[i] = e_pair[tok * KT + k];
             }
-            const float cf = e_coef[tok * KT + k];
-            float *row = S + (m & 0xffffu) * CS + sub * 4;
-            float4 s = *reinterpret_cast<float4 *>(row);
-            if (k < Kw) {
-                s.x = fmaf(cf, xv.x - s.x, s.x);
-                s.y = fmaf(cf, xv.y - s.y, s.y);
-                s.z = fmaf(cf, xv.z - s.z, s.z);
-                s.w = fmaf(cf, xv.w - s.w, s.w);
-                *reinterpret_cast<float4 *>(row) = s;
-            } else {
-                acc.x = fmaf(cf, s.x, acc.x);
-                acc.y = fmaf(cf, s.y, acc.y);
-                acc.z = fmaf(cf, s.z, acc.z);
-                acc.w = fmaf(cf, s.w, acc.w);
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                const uint32_t kind = (pr[i].y >> RN_LINK_KIND_SHIFT) & 7u;  // bit 2: dead
+                if (kind < RN_KIND_HEAD) {
+                    row[i] = *reinterpret_cast<const float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4);
+                } else if (kind <= RN_KIND_LATER && q + (jb + i) * KL >= Kw) {
+                    late |= 1u << (jb + i);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                if (((pr[i].y >> RN_LINK_KIND_SHIFT) & 7u) >= RN_KIND_HEAD) continue;
+                const float cf = __uint_as_float(pr[i].x);
+                if (q + (jb + i) * KL < Kw) {
+                    float4 s = row[i];
+                    s.x = fmaf(cf, xv.x - s.x, s.x);
+                    s.y = fmaf(cf, xv.y - s.y, s.y);
+                    s.z = fmaf(cf, xv.z - s.z, s.z);
+                    s.w = fmaf(cf, xv.w - s.w, s.w);
+                    *reinterpret_cast<float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4) = s;
+                } else {
+                    acc.x = fmaf(cf, row[i].x, acc.x);
+                    acc.y = fmaf(cf, row[i].y, acc.y);
+                    acc.z = fmaf(cf, row[i].z, acc.z);
+                    acc.w = fmaf(cf, row[i].w, acc.w);
+                }
             }
         }
         __syncthreads();
 
-        // ---- rounds 1 .. R-1 from the list: thread -> (entry, channel group) ----------------------------
+        // ---- the chains of this chunk, dealt to the thread groups ----------------------------------------
         {
+            const int n_heads = heads[0];
             const int csub = tid % G;
-            for (int r = 1; r < R; ++r) {
-                const int beg = late_off[r], end = late_off[r + 1];
-                for (int i = beg + tid / G; i < end; i += RN_APPLY_THREADS / G) {
-                    const uint32_t ce = e_late[i];
-                    const int ct = int(ce & 63u), ck = int(ce >> 6);
-                    const int e = ct * KT + ck;
-                    const float cf = e_coef[e];
-                    float *row = S + (e_meta[e] & 0xffffu) * CS + csub * 4;
-                    float4 s = *reinterpret_cast<float4 *>(row);
-                    if (ck < Kw) {
-                        const float4 xr = *reinterpret_cast<const float4 *>(xt + ct * CS + csub * 4);
-                        s.x = fmaf(cf, xr.x - s.x, s.x);
-                        s.y = fmaf(cf, xr.y - s.y, s.y);
-                        s.z = fmaf(cf, xr.z - s.z, s.z);
-                        s.w = fmaf(cf, xr.w - s.w, s.w);
-                        *reinterpret_cast<float4 *>(row) = s;
-                    } else {
+            for (int i = tid / G; i < n_heads; i += RN_APPLY_THREADS / G) {
+                int e = heads[8 + i];
+                uint2 pr = e_pair[e];
+                float *row = S + (pr.y & 0xffffu) * CS + csub * 4;
+                float4 s = *reinterpret_cast<float4 *>(row);
+                bool dirty = false;
+                for (int guard = 0; guard < RN_GSU_NE_MAX; ++guard) {
+                    // the following event's record is requested before this one is applied
+                    const bool more = (pr.y & RN_LINK_NEXT) != 0;
+                    const int en = int((pr.y >> 16) & 0xfffu);
+                    uint2 pr_n = make_uint2(0u, 0u);
+                    if (more) pr_n = e_pair[en];
+                    const float cf = __uint_as_float(pr.x);
+                    const int ct = int(__umulhi(uint32_t(e), kt_magic)), ck = e - ct * KT;
+                    // one instruction stream for writes and reads: the lanes of a warp hold both kinds
+                    const bool wr = ck < Kw;
+                    const float4 xr = *reinterpret_cast<const float4 *>(xt + ct * CS + csub * 4);
+                    if (!wr)
                         *reinterpret_cast<float4 *>(ylate + (ct * Kr + (ck - Kw)) * CS + csub * 4) =
                             make_float4(cf * s.x, cf * s.y, cf * s.z, cf * s.w);
-                    }
+                    const float g = wr ? cf : 0.f;  // a read leaves the row as it is
+                    s.x = fmaf(g, xr.x - s.x, s.x);
+                    s.y = fmaf(g, xr.y - s.y, s.y);
+                    s.z = fmaf(g, xr.z - s.z, s.z);
+                    s.w = fmaf(g, xr.w - s.w, s.w);
+                    dirty |= wr;
+                    if (!more) break;
+                    e = en;
+                    pr = pr_n;
                 }
-                __syncthreads();
+                if (dirty) *reinterpret_cast<float4 *>(row) = s;
             }
         }
+        // the next record (requested at the top of this step) has to be there for the next step
+        if (tid == 0 && has_next && !landed(chunk + 1)) failed = true;
+        if (__syncthreads_or(failed)) {
+            if (tid == 0) atomicExch(p.status, 1);
+            return;
+        }
 
-        // ---- later-round reads of this thread's token, then combine the k-lanes ----------------------------
+        // ---- reads delivered by the chains, then combine the k-lanes ----------------------------------------
 #pragma unroll
         for (int j = 0; j < EV; ++j) {
             if (!(late & (1u << j))) continue;
@@ -542,13 +589,26 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
             const float4 v = *reinterpret_cast<const float4 *>(ylate + (tok * Kr + (k - Kw)) * CS + sub * 4);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        for (int off = G; off < TPT; off <<= 1) {
-            acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
-            acc.y += __shfl_xor_sync(RN_FULL, acc.y, off);
-            acc.z += __shfl_xor_sync(RN_FULL, acc.z, off);
-            acc.w += __shfl_xor_sync(RN_FULL, acc.w, off);
+        if (KL >= 4) {
+            // transposing butterfly over the k-lanes: after two exchange levels lane (q & 3) holds one channel
+            const bool b0 = (q & 1) != 0, b1 = (q & 2) != 0;
+            float k0 = b0 ? acc.z : acc.x, k1 = b0 ? acc.w : acc.y;
+            const float s0 = b0 ? acc.x : acc.z, s1 = b0 ? acc.y : acc.w;
+            k0 += __shfl_xor_sync(RN_FULL, s0, G);
+            k1 += __shfl_xor_sync(RN_FULL, s1, G);
+            float r = b1 ? k1 : k0;
+            r += __shfl_xor_sync(RN_FULL, b1 ? k0 : k1, 2 * G);
+            for (int off = 4 * G; off < TPT; off <<= 1) r += __shfl_xor_sync(RN_FULL, r, off);
+            if (q < 4 && tok_ok && chan_ok) y[int64_t(t0 + tok) * p.yt + (b0 ? 2 : 0) + (b1 ? 1 : 0)] = rn_from_float<T>(r);
+        } else {
+            for (int off = G; off < TPT; off <<= 1) {
+                acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
+                acc.y += __shfl_xor_sync(RN_FULL, acc.y, off);
+                acc.z += __shfl_xor_sync(RN_FULL, acc.z, off);
+                acc.w += __shfl_xor_sync(RN_FULL, acc.w, off);
+            }
+            if (q == 0 && tok_ok && chan_ok) rn_store4<T>(y + int64_t(t0 + tok) * p.yt, acc);
         }
-        if (q == 0 && tok_ok && chan_ok) rn_store4<T>(y + int64_t(t0 + tok) * p.yt, acc);
     }
 
     __syncthreads();
@@ -566,7 +626,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
 constexpr size_t RN_SMEM_BUDGET = 225 * 1024;
 
 static size_t rn_fast_smem(int64_t A, int cs, int NEp, int L, int64_t Kr) {
-    const size_t rec_stride = rn_align(RN_GSU_HDR_BYTES + size_t(NEp) * 10, 128);
+    const size_t rec_stride = rn_align(size_t(NEp) * 9 + 16, 128);  // {coef, link}[], heads[]; double buffered
     return 2 * rec_stride + (size_t(A) * cs + size_t(L) * cs + size_t(L) * Kr * cs) * 4;
 }
 
@@ -596,22 +656,26 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     pl->L = rn_gsu_chunk_len(int(Kw), int(Kr));
     pl->nchunks = int((T + pl->L - 1) / pl->L);
     pl->NE = pl->L * int(Kw + Kr);
-    pl->NEp = int(rn_align(pl->NE, 8));
+    pl->NEp = int(rn_align(pl->NE, 16));
     int ept = (pl->NE + RN_GSU_THREADS - 1) / RN_GSU_THREADS;
     pl->ept = ept <= 1 ? 1 : (ept <= 2 ? 2 : (ept <= 4 ? 4 : (ept <= 8 ? 8 : 16)));
     // schedule kernel: two events per thread (four when a chunk has more than 2048 events)
     pl->sched_ept = pl->NE > 2 * RN_SCHED_THREADS_MAX ? 4 : 2;
     pl->sched_threads = int(rn_align((pl->NE + pl->sched_ept - 1) / pl->sched_ept, 32));
     const size_t ev_bytes = size_t(pl->NE) * 8 + 16;  // mass-aware per-event scratch
-    pl->smem_tables = (size_t(A) * 8 + ev_bytes) <= RN_SMEM_BUDGET;
-    pl->sched_smem = rn_align((pl->smem_tables ? size_t(A) * 8 : 0) + ev_bytes, 16);
+    // mass + claim tables, the successor links of a chunk's events, the latest event of every slot and the
+    // latest chunk in which it had a chain
+    const size_t table_bytes = size_t(A) * 8 + size_t(pl->NEp) * 2 + 2 * rn_align(size_t(A) * 2, 16);
+    pl->smem_tables = (table_bytes + ev_bytes) <= RN_SMEM_BUDGET;
+    pl->sched_smem = rn_align((pl->smem_tables ? table_bytes : 0) + ev_bytes, 16);
     pl->wide = A > 65536;
-    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 14 : 10), 128));
+    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 21 : 17) + 16, 128));
 
     // apply kernel: channels per CTA.  Largest slice that still gives two CTAs per SM of work,
     // else the smallest one (most parallelism).
     const int sms = rn_sm_count(device);
-    const bool fast_ok = !pl->wide && (C % 4) == 0;
+    // the fast kernels walk the per-slot event chains, which only the shared-memory schedule builds
+    const bool fast_ok = !pl->wide && (C % 4) == 0 && pl->smem_tables;
     int best = 0;
     for (int cs = 4; cs <= (fast_ok ? 32 : 128); cs *= 2) {
         int lg = 0;

@@ -18,15 +18,23 @@
 //
 // Chunk record (global workspace, 16-byte aligned, fixed size per call); entry e = t * (Kw+Kr) + k
 // keeps the order of the decoded addresses, so the record is written and read coalesced:
-//   header (272 bytes): u32 R (rounds of this chunk), u32 n_late, then u16 late_off[r] for
-//                   r = 1 .. R: first late[] entry of round r (late_off[R] = n_late)
+//   header (16 bytes): u32 R (rounds of this chunk)
 //   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-23 round, 24 dead (no-op event:
 //                   zero weight or masked token)
 //   f32 coef[NEp]:  gain of a write / weight of a read (mass-aware scaling folded in)
-//   u16 late[NEp]:  the events of round >= 1, sorted by round; an entry is token | k << 6
+//   {f32 coef, u32 link}[NEp]:  the same coefficient next to the event's link word: bits 0-15 slot,
+//                   16-27 the following live event of the chunk on the same slot, 28-29 kind (0 first
+//                   event of its slot in the chunk, 2 second event = head of the slot's chain,
+//                   3 later), 30 dead, 31 has a
+//                   following event (successors are built only when the schedule tables are in shared
+//                   memory)
+//   u16 heads[8 + NEp/2]:  heads[0] = number of chains, heads[8..] their head events, chains of three or
+//                   more events first, then those of two, then those of one
 //   u32 slot[NEp]:  only in the wide format (A > 65536)
-// Round 0 holds ~80 % of the events of a chunk and is applied token-major (dense); the later,
-// sparse rounds are applied from the late[] list so every lane has work.
+// The first events (~80 % of a chunk) are applied token-major (dense).  The later events of a slot
+// form a chain (head, then link by link); the fast apply kernel walks a chain with the slot row in
+// registers.  The backward sweeps and the general apply kernel go round by round over meta[]
+// instead.
 #pragma once
 
 #include "rn_common.cuh"
@@ -37,9 +45,12 @@ constexpr int RN_SCHED_THREADS_MAX = 1024;        // schedule kernel: 2 events p
 constexpr int RN_GSU_LMAX = 64;                   // longest time chunk
 constexpr int RN_GSU_NE_MAX = 4096;               // most events per chunk (L * (Kw + Kr))
 constexpr int RN_GSU_RMAX = 2 * RN_GSU_LMAX;      // most rounds in a chunk
-constexpr int RN_GSU_HDR_BYTES = 272;            // 8 + 2 * (RN_GSU_RMAX + 2), rounded up to 16
+constexpr int RN_GSU_HDR_BYTES = 16;
 
 constexpr uint32_t RN_EV_DEAD = 1u << 24;
+constexpr uint32_t RN_LINK_DEAD = 1u << 30, RN_LINK_NEXT = 1u << 31;
+constexpr int RN_LINK_KIND_SHIFT = 28;
+constexpr uint32_t RN_KIND_FIRST = 0, RN_KIND_HEAD = 2, RN_KIND_LATER = 3;
 
 __host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int round, bool dead) {
     return (slot16 & 0xffffu) | (uint32_t(round & 0xff) << 16) | (dead ? RN_EV_DEAD : 0u);
