@@ -326,6 +326,13 @@ extern "C" int rn_addr_bwd(const int32_t *idx, const float *val, const int64_t *
     RnDeviceGuard guard(device);
     RN_REQUIRE(guard.ok, "cannot make device %d current", device);
 
+    if (rn_addr_bwd_fast(idx, val, out_strides, d_val, dval_strides, w_addr, r_addr, dtype, addr_strides, pos, pos_strides,
+                         d_w, d_r, dgrad_strides, B, H, U, P, T, E, A, Kw, Kr, w_re_norm, r_re_norm, w_neg, r_neg,
+                         cudaStream_t(stream)) == 0) {
+        RN_CUDA(cudaGetLastError());
+        return 0;
+    }
+
     RnAddrBwdParams p{};
     p.idx = idx; p.val = val;
     p.ob = out_strides[0]; p.oh = out_strides[1]; p.ok = out_strides[2]; p.ot = out_strides[3];

@@ -232,3 +232,9 @@ int rn_addr_fwd_fast(const void *w_addr, const void *r_addr, int dtype, const in
                      const int64_t *pos_strides, int32_t *idx, float *val, const int64_t *out_strides, int64_t B,
                      int64_t H, int64_t U, int64_t P, int64_t T, int64_t E, int64_t A, int64_t Kw, int64_t Kr,
                      double w_re_norm, double r_re_norm, int w_neg, int r_neg, int encode_batch, cudaStream_t stream);
+int rn_addr_bwd_fast(const int32_t *idx, const float *val, const int64_t *out_strides, const float *d_val,
+                     const int64_t *dval_strides, const void *w_addr, const void *r_addr, int dtype,
+                     const int64_t *addr_strides, const int32_t *pos, const int64_t *pos_strides, void *d_w, void *d_r,
+                     const int64_t *dgrad_strides, int64_t B, int64_t H, int64_t U, int64_t P, int64_t T, int64_t E,
+                     int64_t A, int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm, int w_neg, int r_neg,
+                     cudaStream_t stream);

@@ -106,14 +106,20 @@ def test_inactive_and_extreme_logits():
 
 @pytest.mark.parametrize("shape", SHAPES[:6])
 @pytest.mark.parametrize("renorm", [0.0, 0.5, 1.0])
-def test_backward_matches_oracle_autograd(shape, renorm):
+@pytest.mark.parametrize("token_major", [False, True])
+def test_backward_matches_oracle_autograd(shape, renorm, token_major):
+    """token_major: the gradient of the weights laid out like the weights themselves (K entries of a
+    token-head contiguous), which is what the prefill backward hands over and what the specialised
+    backward kernel takes; otherwise (B,H,K,T)-contiguous, which only the general kernel takes."""
     ops()
     B, H, U, P, T, K, E, dtype, std = shape
     addr, pos = _case(*shape, seed=1)
+    if token_major:
+        addr[0, 1] = float("-inf")           # an inactive token: zero gradient
     view = addr.permute(0, 2, 3, 4, 1)
     dev = view.cuda()
     idx, val = torch.ops.ramnet_ops.topk_addr_single_forward(dev, E, P ** U, pos.cuda(), K, renorm, False, True)
-    d_val = randn((B, H, K, T), 2)
+    d_val = randn((B, T, H, K), 2).permute(0, 2, 3, 1) if token_major else randn((B, H, K, T), 2)
     got = torch.ops.ramnet_ops.topk_addr_single_backward(idx, val, dev, d_val.cuda(), E, pos.cuda(), K, renorm, False,
                                                          [B, H, U, P, P ** U, T], dtype)
     assert got.shape == view.shape and got.dtype == dtype
