@@ -8,6 +8,8 @@
 //
 // State offsets are 64-bit: B*H*A*C may exceed 2^31 elements.
 #include "rn_addr_fast.cuh"
+#include "rn_addr_half.cuh"
+#include "rn_prefill.cuh"
 #include "rn_gsu.cuh"
 
 constexpr int RN_DEC_WARPS = 4;
@@ -199,22 +201,32 @@ __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDe
 // Warps 0-3 decode the 32 addresses of the CTA (16 pairs x write/read logits), four lanes per
 // address, with the register-resident sorting networks of rn_addr_fast.cuh: a warp instruction
 // serves 8 addresses and the dependent chain of one address is short enough to hide behind the
-// row traffic of the other resident CTA.  Then warp w owns pairs 2w and 2w+1: it loads the K
-// write rows of a pair at once (K 512-byte loads in flight), updates and stores them, then loads
-// the K read rows, reduces them in registers and applies the epilogue.  A lane always re-reads
-// exactly the 16 bytes of a row that it wrote itself, so no barrier separates writes from reads.
+// row traffic of the other resident CTA.  Then warp w owns pairs 2w and 2w+1.  The K write rows of
+// a pair travel by 1-D bulk async copies: global -> this warp's shared-memory buffer (one mbarrier
+// per warp, bounded wait), update in shared memory, shared -> global.  Random 512-byte rows fetched
+// this way reach about twice the bandwidth of per-lane loads, whose outstanding requests per SM run
+// out first.  The K read rows are loaded into registers at the same time; a read row that is also a
+// write row of this step is taken from the updated copy in shared memory instead.
 constexpr int RN_DECF_PAIRS = 16;
 constexpr int RN_DECF_THREADS = 256;
 
 template <typename T, int U, int P, int K, int NV>
 __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(const RnDecodeParams p) {
+    extern __shared__ __align__(128) unsigned char row_bytes_buf[];  // per warp: K rows of C floats
     __shared__ int sel_slot[RN_DECF_PAIRS][2][K];
     __shared__ float sel_val[RN_DECF_PAIRS][2][K];
+    __shared__ __align__(8) uint64_t mbar[RN_DECF_THREADS / 32];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int BH = p.B * p.H;
     const int bh0 = blockIdx.x * RN_DECF_PAIRS;
     const int C = p.C;
+    constexpr uint32_t ROW_BYTES = NV * 512;
+    float *wbuf = reinterpret_cast<float *>(row_bytes_buf) + size_t(warp) * K * (NV * 128);
+    if (lane == 0) {
+        rn_mbar_init(&mbar[warp], 1);
+        rn_mbar_fence_init();
+    }
 
     if (warp < 4) {
         // four lanes per address: 32 addresses (16 pairs x write/read) on warps 0-3
@@ -237,6 +249,7 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
     }
     __syncthreads();
 
+    uint32_t phase = 0;  // parity of this warp's mbarrier
 #pragma unroll 1
     for (int pp = 0; pp < 2; ++pp) {
         const int pair = warp * 2 + pp;
@@ -256,42 +269,76 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
 #pragma unroll
         for (int v = 0; v < NV; ++v) xv[v] = rn_load4<T>(static_cast<const T *>(p.x) + int64_t(bh) * C + v * 128 + lane * 4);
 
-        // ---- writes -----------------------------------------------------------------------------
-        {
-            const int a_l = lane < K ? sel_slot[pair][0][lane] : 0;
-            const float w_l = lane < K ? sel_val[pair][0][lane] : 0.f;
-            float gain_l = 0.f;
-            float4 rows[K][NV];
+        // ---- write rows: bulk copies into this warp's buffer -------------------------------------------
+        const int a_l = lane < K ? sel_slot[pair][0][lane] : 0;
+        const float w_l = lane < K ? sel_val[pair][0][lane] : 0.f;
+        const bool live_w = lane < K && w_l != 0.f;
+        const int nlive = __popc(__ballot_sync(RN_FULL, live_w));
+        if (nlive > 0) {
+            if (lane == 0) rn_mbar_expect_tx(&mbar[warp], uint32_t(nlive) * ROW_BYTES);
+            __syncwarp();
+            if (live_w) rn_bulk_g2s(wbuf + lane * (NV * 128), slot + int64_t(a_l) * C, ROW_BYTES, &mbar[warp]);
+        }
+
+        // ---- read rows: per-lane loads into registers, in flight together with the bulk copies -------------
+        const int ar_l = lane < K ? sel_slot[pair][1][lane] : 0;
+        float r_l = lane < K ? sel_val[pair][1][lane] : 0.f;
+        float4 rows[K][NV];
 #pragma unroll
-            for (int k = 0; k < K; ++k) {
-                const int a = __shfl_sync(RN_FULL, a_l, k);
+        for (int k = 0; k < K; ++k) {
+            const int a = __shfl_sync(RN_FULL, ar_l, k);
 #pragma unroll
-                for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
-            }
-            if (lane < K && w_l != 0.f) {
-                const RnGate g = rn_gate(w_l, gamma, mass[a_l], p.eps);
-                gain_l = g.gain;
-                mass[a_l] = g.mass;
-            }
+            for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
+        }
+        // a read row that this step also writes: index of that write row, else -1
+        int alias_l = -1;
 #pragma unroll
-            for (int k = 0; k < K; ++k) {
-                const int a = __shfl_sync(RN_FULL, a_l, k);
-                const float w = __shfl_sync(RN_FULL, w_l, k);
-                const float gain = __shfl_sync(RN_FULL, gain_l, k);
-                if (w != 0.f) {
+        for (int j = 0; j < K; ++j) {
+            const int aw = __shfl_sync(RN_FULL, a_l, j);
+            const float ww = __shfl_sync(RN_FULL, w_l, j);
+            if (ww != 0.f && aw == ar_l) alias_l = j;
+        }
+        float gain_l = 0.f;
+        if (live_w) {
+            const RnGate g = rn_gate(w_l, gamma, mass[a_l], p.eps);
+            gain_l = g.gain;
+            mass[a_l] = g.mass;
+        }
+        __syncwarp();
+
+        bool landed = true;
+        if (nlive > 0) {
+            landed = rn_mbar_wait_bounded(&mbar[warp], phase);
+            phase ^= 1u;
+        }
+        if (!__all_sync(RN_FULL, landed)) {
+            // a bulk copy never completed: leave the state alone, make the failure visible in the output,
+            // and stop using the buffer (the copy may still land)
 #pragma unroll
-                    for (int v = 0; v < NV; ++v) {
-                        float4 s = rows[k][v];
-                        s.x = fmaf(gain, xv[v].x - s.x, s.x);
-                        s.y = fmaf(gain, xv[v].y - s.y, s.y);
-                        s.z = fmaf(gain, xv[v].z - s.z, s.z);
-                        s.w = fmaf(gain, xv[v].w - s.w, s.w);
-                        *reinterpret_cast<float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4) = s;
-                    }
+            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(NAN, NAN, NAN, NAN));
+            break;
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const float w = __shfl_sync(RN_FULL, w_l, k);
+            const float gain = __shfl_sync(RN_FULL, gain_l, k);
+            if (w != 0.f) {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    float4 *cell = reinterpret_cast<float4 *>(wbuf + k * (NV * 128) + v * 128 + lane * 4);
+                    float4 s = *cell;
+                    s.x = fmaf(gain, xv[v].x - s.x, s.x);
+                    s.y = fmaf(gain, xv[v].y - s.y, s.y);
+                    s.z = fmaf(gain, xv[v].z - s.z, s.z);
+                    s.w = fmaf(gain, xv[v].w - s.w, s.w);
+                    *cell = s;
                 }
             }
         }
+        rn_fence_proxy_async();  // the updated rows are read by the bulk copy engine next
         __syncwarp();
+        if (live_w) rn_bulk_s2g(slot + int64_t(a_l) * C, wbuf + lane * (NV * 128), ROW_BYTES);
+        rn_bulk_commit();
 
         // ---- reads (after the writes of this step) ---------------------------------------------------
         float4 acc[NV];
@@ -299,17 +346,8 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
         for (int v = 0; v < NV; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
         float scale = 1.f;
         {
-            const int a_l = lane < K ? sel_slot[pair][1][lane] : 0;
-            float r_l = lane < K ? sel_val[pair][1][lane] : 0.f;
-            float4 rows[K][NV];
-#pragma unroll
-            for (int k = 0; k < K; ++k) {
-                const int a = __shfl_sync(RN_FULL, a_l, k);
-#pragma unroll
-                for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
-            }
             if (p.mass_aware) {
-                const float rm = (lane < K && r_l != 0.f) ? r_l * mass[a_l] : 0.f;
+                const float rm = (lane < K && r_l != 0.f) ? r_l * mass[ar_l] : 0.f;
                 const float sr = rn_warp_sum(lane < K ? r_l : 0.f), srm = rn_warp_sum(rm);
                 scale = sr / (srm + p.eps);
                 r_l = rm;
@@ -317,17 +355,22 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
 #pragma unroll
             for (int k = K - 1; k >= 0; --k) {
                 const float coef = __shfl_sync(RN_FULL, r_l, k);
+                const int al = __shfl_sync(RN_FULL, alias_l, k);
                 if (coef != 0.f) {
 #pragma unroll
                     for (int v = 0; v < NV; ++v) {
-                        acc[v].x = fmaf(coef, rows[k][v].x, acc[v].x);
-                        acc[v].y = fmaf(coef, rows[k][v].y, acc[v].y);
-                        acc[v].z = fmaf(coef, rows[k][v].z, acc[v].z);
-                        acc[v].w = fmaf(coef, rows[k][v].w, acc[v].w);
+                        float4 s = rows[k][v];
+                        if (al >= 0) s = *reinterpret_cast<const float4 *>(wbuf + al * (NV * 128) + v * 128 + lane * 4);
+                        acc[v].x = fmaf(coef, s.x, acc[v].x);
+                        acc[v].y = fmaf(coef, s.y, acc[v].y);
+                        acc[v].z = fmaf(coef, s.z, acc[v].z);
+                        acc[v].w = fmaf(coef, s.w, acc[v].w);
                     }
                 }
             }
         }
+        rn_bulk_wait_read();  // the buffer is free again once the outgoing copies have read it
+        __syncwarp();
         float sq = 0.f;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
@@ -355,24 +398,251 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// decode step, one warp per (b,h) pair: U = 2, P = 64, K = 16, 16-bit logits
+// ------------------------------------------------------------------------------------------
+// The two halves of a warp decode the write and the read address of the pair with the
+// sixteen-lanes-per-row decoder (rn_addr_half.cuh; a dependent chain of ~2 us instead of ~14 us),
+// then the same warp moves the rows: the 16 write rows by 1-D bulk async copies through its
+// shared-memory buffer (global -> shared, update, shared -> global), the 16 read rows by per-lane
+// loads into registers at the same time; a read row that is also written in this step is taken
+// from the updated copy in shared memory.  Warps are independent (no CTA barrier), so the address
+// decode of some pairs overlaps the row traffic of others; a CTA's warps walk the pairs with a
+// grid-wide stride.
+constexpr int RN_DECP_THREADS = 256;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(const RnDecodeParams p) {
+    constexpr int U = 2, P = 64, K = 16;
+    extern __shared__ __align__(128) unsigned char row_bytes_buf[];  // per warp: K rows of C floats
+    __shared__ __align__(8) uint64_t mbar[RN_DECP_THREADS / 32];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, hl = lane & 15;
+    const int BH = p.B * p.H;
+    constexpr int C = NV * 128;
+    constexpr uint32_t ROW_BYTES = C * 4;
+    float *wbuf = reinterpret_cast<float *>(row_bytes_buf) + size_t(warp) * K * C;
+    if (lane == 0) {
+        rn_mbar_init(&mbar[warp], 1);
+        rn_mbar_fence_init();
+    }
+    __syncwarp();
+    const uint32_t cand = rn_half::load_candidates(hl);
+    const int which = lane >> 4;  // lower half: write address, upper half: read address
+    uint32_t phase = 0;           // parity of this warp's mbarrier
+
+#pragma unroll 1
+    for (int bh = blockIdx.x * (RN_DECP_THREADS / 32) + warp; bh < BH; bh += gridDim.x * (RN_DECP_THREADS / 32)) {
+        const int b = bh / p.H, h = bh % p.H;
+        T *y = static_cast<T *>(p.y) + int64_t(bh) * C;
+        if (p.mask != nullptr && p.mask[b] == 0) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+            continue;
+        }
+        float *slot = p.slot + int64_t(bh) * p.A * C;
+        float *mass = p.mass + int64_t(bh) * p.A;
+
+        // inputs that do not depend on the addresses are requested first
+        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[bh]);
+        const int shift = (h < p.E) ? rn_pos_mod(p.pos[b], p.A) : 0;
+        RnRaw4<T> xraw[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) xraw[v] = rn_load_raw4<T>(static_cast<const T *>(p.x) + int64_t(bh) * C + v * 128 + lane * 4);
+
+        // ---- both addresses of the pair --------------------------------------------------------------
+        int content;
+        float weight;
+        rn_half::decode_u2p64k16<T>(static_cast<const T *>(which ? p.r_addr : p.w_addr) + int64_t(bh) * U * P, p.re_norm[which],
+                                    lane, cand, content, weight);
+        const int my_slot = rn_cape(content, shift, p.A);
+        // lanes 0-15: entry `lane` of the write address; their read entry comes from the upper half
+        const int a_l = my_slot;
+        const float w_l = lane < K ? weight : 0.f;
+        const int ar_l = __shfl_down_sync(RN_FULL, my_slot, 16);
+        float r_l = __shfl_down_sync(RN_FULL, weight, 16);
+        if (lane >= K) r_l = 0.f;
+
+        // ---- write rows: bulk copies into this warp's buffer -------------------------------------------
+        const bool live_w = lane < K && w_l != 0.f;
+        const float mass_l = live_w ? mass[a_l] : 0.f;  // requested before the row traffic
+        const int nlive = __popc(__ballot_sync(RN_FULL, live_w));
+        if (nlive > 0) {
+            if (lane == 0) rn_mbar_expect_tx(&mbar[warp], uint32_t(nlive) * ROW_BYTES);
+            __syncwarp();
+            if (live_w) rn_bulk_g2s(wbuf + lane * C, slot + int64_t(a_l) * C, ROW_BYTES, &mbar[warp]);
+        }
+
+        // ---- read rows: per-lane loads into registers, in flight together with the bulk copies -------------
+        float4 rows[K][NV];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const int a = __shfl_sync(RN_FULL, ar_l, k);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
+        }
+        // a read row that this step also writes: index of that write row, else -1.  All 32 lanes hold a slot
+        // (lower half write, upper half read): one match finds the equal ones.
+        const unsigned live_mask = __ballot_sync(RN_FULL, live_w);
+        const unsigned same = __match_any_sync(RN_FULL, my_slot) & live_mask;  // live write lanes with this lane's slot
+        const int alias_up = same ? __ffs(same) - 1 : -1;
+        const int alias_l = __shfl_down_sync(RN_FULL, alias_up, 16);
+        float gain_l = 0.f;
+        if (live_w) {
+            const RnGate g = rn_gate(w_l, gamma, mass_l, p.eps);
+            gain_l = g.gain;
+            mass[a_l] = g.mass;
+        }
+        __syncwarp();
+        float4 xv[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) xv[v] = rn_cvt_raw4(xraw[v]);
+
+        bool landed = true;
+        if (nlive > 0) {
+            landed = rn_mbar_wait_bounded(&mbar[warp], phase);
+            phase ^= 1u;
+        }
+        if (!__all_sync(RN_FULL, landed)) {
+            // a bulk copy never completed: leave the state alone, make the failure visible in the output,
+            // and stop using the buffer (the copy may still land)
+#pragma unroll
+            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(NAN, NAN, NAN, NAN));
+            break;
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            const float gain = __shfl_sync(RN_FULL, gain_l, k);
+            if (live_mask & (1u << k)) {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    float4 *cell = reinterpret_cast<float4 *>(wbuf + k * C + v * 128 + lane * 4);
+                    float4 s = *cell;
+                    s.x = fmaf(gain, xv[v].x - s.x, s.x);
+                    s.y = fmaf(gain, xv[v].y - s.y, s.y);
+                    s.z = fmaf(gain, xv[v].z - s.z, s.z);
+                    s.w = fmaf(gain, xv[v].w - s.w, s.w);
+                    *cell = s;
+                }
+            }
+        }
+        rn_fence_proxy_async();  // the updated rows are read by the bulk copy engine next
+        __syncwarp();
+        if (live_w) rn_bulk_s2g(slot + int64_t(a_l) * C, wbuf + lane * C, ROW_BYTES);
+        rn_bulk_commit();
+
+        // ---- reads (after the writes of this step) ---------------------------------------------------
+        float4 acc[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float scale = 1.f;
+        if (p.mass_aware) {
+            const float rm = (lane < K && r_l != 0.f) ? r_l * mass[ar_l] : 0.f;
+            const float sr = rn_warp_sum(lane < K ? r_l : 0.f), srm = rn_warp_sum(rm);
+            scale = sr / (srm + p.eps);
+            r_l = rm;
+        }
+#pragma unroll
+        for (int k = K - 1; k >= 0; --k) {
+            const float coef = __shfl_sync(RN_FULL, r_l, k);
+            const int al = __shfl_sync(RN_FULL, alias_l, k);
+            if (coef != 0.f) {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    float4 s = rows[k][v];
+                    if (al >= 0) s = *reinterpret_cast<const float4 *>(wbuf + al * C + v * 128 + lane * 4);
+                    acc[v].x = fmaf(coef, s.x, acc[v].x);
+                    acc[v].y = fmaf(coef, s.y, acc[v].y);
+                    acc[v].z = fmaf(coef, s.z, acc[v].z);
+                    acc[v].w = fmaf(coef, s.w, acc[v].w);
+                }
+            }
+        }
+        float sq = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            acc[v].x *= scale; acc[v].y *= scale; acc[v].z *= scale; acc[v].w *= scale;
+            sq += acc[v].x * acc[v].x + acc[v].y * acc[v].y + acc[v].z * acc[v].z + acc[v].w * acc[v].w;
+        }
+        if (p.norm_weight != nullptr) {
+            const float inv_rms = rsqrtf(rn_warp_sum(sq) / float(C) + p.norm_eps);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const float4 nw = *reinterpret_cast<const float4 *>(p.norm_weight + v * 128 + lane * 4);
+                acc[v].x *= inv_rms * nw.x; acc[v].y *= inv_rms * nw.y; acc[v].z *= inv_rms * nw.z; acc[v].w *= inv_rms * nw.w;
+            }
+        }
+        if (p.gate != nullptr) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + int64_t(bh) * C + v * 128 + lane * 4);
+                acc[v].x /= 1.f + expf(-gl.x); acc[v].y /= 1.f + expf(-gl.y);
+                acc[v].z /= 1.f + expf(-gl.z); acc[v].w /= 1.f + expf(-gl.w);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, acc[v]);
+        rn_bulk_wait_read();  // the buffer is free again once the outgoing copies have read it
+        __syncwarp();
+    }
+}
+
+// 0 = launched, -1 = not this kernel's shape
+template <typename T>
+static int rn_launch_decode_pair(const RnDecodeParams &p, int device, cudaStream_t stream) {
+    if constexpr (rn_fast::Raw<T>::wide) {
+        return -1;
+    } else {
+        if (!(p.U == 2 && p.P == 64 && p.K[0] == 16 && p.K[1] == 16)) return -1;
+        const int wpc = RN_DECP_THREADS / 32;
+        const int want = (p.B * p.H + wpc - 1) / wpc;
+        const int cap = 2 * rn_sm_count(device);  // two resident CTAs per SM; the warps stride over the pairs
+        const int grid = want < cap ? want : cap;
+        if (p.C == 128) {
+            constexpr int smem = (RN_DECP_THREADS / 32) * 16 * 128 * 4;
+            if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+            rn_decode_pair_kernel<T, 1><<<grid, RN_DECP_THREADS, smem, stream>>>(p);
+        } else if (p.C == 256) {
+            constexpr int smem = (RN_DECP_THREADS / 32) * 16 * 256 * 4;
+            if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+            rn_decode_pair_kernel<T, 2><<<grid, RN_DECP_THREADS, smem, stream>>>(p);
+        } else {
+            return -1;
+        }
+        return 0;
+    }
+}
+
 template <typename T, int U, int P, int K>
 static int rn_launch_decode_fast_c(const RnDecodeParams &p, cudaStream_t stream) {
     const int grid = (p.B * p.H + RN_DECF_PAIRS - 1) / RN_DECF_PAIRS;
-    if (p.C == 128) rn_decode_fast_kernel<T, U, P, K, 1><<<grid, RN_DECF_THREADS, 0, stream>>>(p);
-    else if (p.C == 256) rn_decode_fast_kernel<T, U, P, K, 2><<<grid, RN_DECF_THREADS, 0, stream>>>(p);
-    else return -1;
+    // dynamic shared memory: one buffer of K rows per warp
+    if (p.C == 128) {
+        constexpr int smem = (RN_DECF_THREADS / 32) * K * 128 * 4;
+        if (cudaFuncSetAttribute(rn_decode_fast_kernel<T, U, P, K, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return -1;
+        rn_decode_fast_kernel<T, U, P, K, 1><<<grid, RN_DECF_THREADS, smem, stream>>>(p);
+    } else if (p.C == 256) {
+        constexpr int smem = (RN_DECF_THREADS / 32) * K * 256 * 4;
+        if (cudaFuncSetAttribute(rn_decode_fast_kernel<T, U, P, K, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return -1;
+        rn_decode_fast_kernel<T, U, P, K, 2><<<grid, RN_DECF_THREADS, smem, stream>>>(p);
+    } else {
+        return -1;
+    }
     return 0;
 }
 
 // 0 = launched, -1 = no specialised kernel for this shape
 template <typename T>
-static int rn_launch_decode_fast(const RnDecodeParams &p, cudaStream_t stream) {
+static int rn_launch_decode_fast(const RnDecodeParams &p, int device, cudaStream_t stream) {
     if (p.K[0] != p.K[1]) return -1;
     const size_t esz = sizeof(T);
     const uintptr_t io = reinterpret_cast<uintptr_t>(p.w_addr) | reinterpret_cast<uintptr_t>(p.r_addr) |
                          reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y) |
                          reinterpret_cast<uintptr_t>(p.gate) | reinterpret_cast<uintptr_t>(p.norm_weight);
     if ((io & 15) != 0 || (size_t(p.U) * p.P * esz) % 16 != 0) return -1;
+    if (rn_launch_decode_pair<T>(p, device, stream) == 0) return 0;
     if (p.U == 2 && p.P == 64 && p.K[0] == 16) return rn_launch_decode_fast_c<T, 2, 64, 16>(p, stream);
     if (p.U == 3 && p.P == 32 && p.K[0] == 8) return rn_launch_decode_fast_c<T, 3, 32, 8>(p, stream);
     if (p.U == 2 && p.P == 16 && p.K[0] == 4) return rn_launch_decode_fast_c<T, 2, 16, 4>(p, stream);
@@ -437,9 +707,9 @@ extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void
     int rc;
     rn_prof_reset();
     rn_prof_mark(cudaStream_t(stream));
-    rc = dtype == RN_F32 ? rn_launch_decode_fast<float>(p, cudaStream_t(stream))
-         : dtype == RN_F16 ? rn_launch_decode_fast<__half>(p, cudaStream_t(stream))
-                           : rn_launch_decode_fast<__nv_bfloat16>(p, cudaStream_t(stream));
+    rc = dtype == RN_F32 ? rn_launch_decode_fast<float>(p, device, cudaStream_t(stream))
+         : dtype == RN_F16 ? rn_launch_decode_fast<__half>(p, device, cudaStream_t(stream))
+                           : rn_launch_decode_fast<__nv_bfloat16>(p, device, cudaStream_t(stream));
     if (rc == 0) {
         RN_CUDA(cudaGetLastError());
         rn_prof_mark(cudaStream_t(stream));

@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     __shared__ float gam[2][RN_GSU_LMAX];
     __shared__ float tok_scale[RN_GSU_LMAX];
     __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
-    __shared__ int n_heads[4];  // chains with >= 3, 2, 1 events after the first; then the running offsets
+    __shared__ int n_heads;
 
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
@@ -23,12 +23,11 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     const int A = p.A, KT = p.Kw + p.Kr, NEp = p.NEp;
     const bool pow2 = (A & (A - 1)) == 0;
 
-    // dynamic smem: [mass A][claim A][nxt NEp][last A][clen A] (SMEM_TABLES) | ev_v[NE] ev_c[NE] (mass-aware only)
+    // dynamic smem: [mass A][claim A][nxt NEp][last A] (SMEM_TABLES) | ev_v[NE] ev_c[NE] (mass-aware only)
     unsigned char *cur = dyn;
     float *mass;
     uint32_t *claim;
-    // successor of every event on its slot; latest event of every slot; events after the first on a slot
-    uint16_t *nxt = nullptr, *last = nullptr, *clen = nullptr;
+    uint16_t *nxt = nullptr, *last = nullptr;  // successor of every event on its slot; latest event of every slot
     if (SMEM_TABLES) {
         mass = reinterpret_cast<float *>(cur);
         cur += size_t(A) * 4;
@@ -37,8 +36,6 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         nxt = reinterpret_cast<uint16_t *>(cur);
         cur += size_t(NEp) * 2;
         last = reinterpret_cast<uint16_t *>(cur);
-        cur += (size_t(A) * 2 + 15) / 16 * 16;
-        clen = reinterpret_cast<uint16_t *>(cur);
         cur += (size_t(A) * 2 + 15) / 16 * 16;
     } else {
         mass = p.mass_out + int64_t(bh) * A;
@@ -102,7 +99,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         float ev[EPT], ec[EPT], em[EPT];  // slot, weight, coefficient, mass before the write
         int er[EPT];          // round, or -1 dead (zero weight / masked token), -3 out of range
         uint32_t pend = 0;
-        if (tid < 4) n_heads[tid] = 0;
+        if (tid == 0) n_heads = 0;
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             er[j] = -3;
@@ -142,7 +139,6 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                     if (SMEM_TABLES) {  // link the slot's events in time order (one winner per slot and round)
                         if (R > 0) nxt[last[ea[j]]] = uint16_t(j * NT + tid);
                         last[ea[j]] = uint16_t(j * NT + tid);
-                        if (R > 0) clen[ea[j]] = uint16_t(R);  // ends as the length of the slot's chain
                     }
                     er[j] = R;
                     claim[ea[j]] = 0xffffffffu;
@@ -186,44 +182,17 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         uint16_t *o_heads = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 16);
         uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 17 + 16);
         if (tid == 0) reinterpret_cast<uint32_t *>(rec)[0] = uint32_t(R);
-        // chain heads (round-1 events), the longest chains first so that the threads of a warp of the apply
-        // kernel walk chains of equal length: three classes, warp-aggregated counting then placement
-        int hcls[EPT];
+        // chain heads (round-1 events) in any order: warp-aggregated append
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            hcls[j] = -1;
-            if (er[j] == 1) {
-                const int len = SMEM_TABLES ? int(clen[ea[j]]) : 1;
-                hcls[j] = len >= 3 ? 0 : (len == 2 ? 1 : 2);
-            }
-#pragma unroll
-            for (int c = 0; c < 3; ++c) {
-                const unsigned act = __ballot_sync(RN_FULL, hcls[j] == c);
-                if (act != 0u && (tid & 31) == __ffs(act) - 1) atomicAdd(&n_heads[c], __popc(act));
-            }
-        }
-        __syncthreads();
-        if (tid == 0) {
-            const int n0 = n_heads[0], n1 = n_heads[1], n2 = n_heads[2];
-            n_heads[0] = 0;
-            n_heads[1] = n0;
-            n_heads[2] = n0 + n1;
-            o_heads[0] = uint16_t(n0 + n1 + n2);
-        }
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-#pragma unroll
-            for (int c = 0; c < 3; ++c) {
-                const bool emit = hcls[j] == c;
-                const unsigned act = __ballot_sync(RN_FULL, emit);
-                if (act != 0u) {
-                    const int lane = tid & 31, leader = __ffs(act) - 1;
-                    int base = 0;
-                    if (lane == leader) base = atomicAdd(&n_heads[c], __popc(act));
-                    base = __shfl_sync(RN_FULL, base, leader);
-                    if (emit) o_heads[8 + base + __popc(act & ((1u << lane) - 1u))] = uint16_t(j * NT + tid);
-                }
+            const bool emit = er[j] == 1;
+            const unsigned act = __ballot_sync(RN_FULL, emit);
+            if (act != 0u) {
+                const int lane = tid & 31, leader = __ffs(act) - 1;
+                int base = 0;
+                if (lane == leader) base = atomicAdd(&n_heads, __popc(act));
+                base = __shfl_sync(RN_FULL, base, leader);
+                if (emit) o_heads[8 + base + __popc(act & ((1u << lane) - 1u))] = uint16_t(j * NT + tid);
             }
         }
 #pragma unroll
@@ -244,6 +213,8 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 if (p.wide) o_slot[e] = ea[j];
             }
         }
+        __syncthreads();  // n_heads is complete
+        if (tid == 0) o_heads[0] = uint16_t(n_heads);
         if (p.prev_mass != nullptr) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
@@ -663,9 +634,8 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     pl->sched_ept = pl->NE > 2 * RN_SCHED_THREADS_MAX ? 4 : 2;
     pl->sched_threads = int(rn_align((pl->NE + pl->sched_ept - 1) / pl->sched_ept, 32));
     const size_t ev_bytes = size_t(pl->NE) * 8 + 16;  // mass-aware per-event scratch
-    // mass + claim tables, the successor links of a chunk's events, the latest event of every slot and the
-    // latest chunk in which it had a chain
-    const size_t table_bytes = size_t(A) * 8 + size_t(pl->NEp) * 2 + 2 * rn_align(size_t(A) * 2, 16);
+    // mass + claim tables, the successor links of a chunk's events and the latest event of every slot
+    const size_t table_bytes = size_t(A) * 8 + size_t(pl->NEp) * 2 + rn_align(size_t(A) * 2, 16);
     pl->smem_tables = (table_bytes + ev_bytes) <= RN_SMEM_BUDGET;
     pl->sched_smem = rn_align((pl->smem_tables ? table_bytes : 0) + ev_bytes, 16);
     pl->wide = A > 65536;

@@ -28,8 +28,7 @@
 //                   3 later), 30 dead, 31 has a
 //                   following event (successors are built only when the schedule tables are in shared
 //                   memory)
-//   u16 heads[8 + NEp/2]:  heads[0] = number of chains, heads[8..] their head events, chains of three or
-//                   more events first, then those of two, then those of one
+//   u16 heads[8 + NEp/2]:  heads[0] = number of chains, heads[8..] their head events in any order
 //   u32 slot[NEp]:  only in the wide format (A > 65536)
 // The first events (~80 % of a chunk) are applied token-major (dense).  The later events of a slot
 // form a chain (head, then link by link); the fast apply kernel walks a chain with the slot row in
@@ -153,6 +152,14 @@ __device__ __forceinline__ bool rn_mbar_wait_bounded(uint64_t *bar, uint32_t par
     }
     return true;
 }
+// shared -> global bulk copy (one bulk group per commit); wait_read returns once the copies of this thread's
+// groups have read their shared-memory source
+__device__ __forceinline__ void rn_bulk_s2g(void *dst, const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(rn_smem_u32(src)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void rn_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void rn_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void rn_bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      rn_smem_u32(dst)),
