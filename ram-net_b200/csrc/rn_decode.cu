@@ -412,6 +412,11 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
 constexpr int RN_DECP_THREADS = 256;
 
 template <typename T, int NV>
+__device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
+                                                    const int which, const uint32_t cand, float *wbuf, uint64_t *bar,
+                                                    uint32_t &phase);
+
+template <typename T, int NV>
 __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(const RnDecodeParams p) {
     constexpr int U = 2, P = 64, K = 16;
     extern __shared__ __align__(128) unsigned char row_bytes_buf[];  // per warp: K rows of C floats
@@ -431,14 +436,40 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
     const int which = lane >> 4;  // lower half: write address, upper half: read address
     uint32_t phase = 0;           // parity of this warp's mbarrier
 
+    // This CTA's share of the pairs (equal shares, so every SM gets the same work); its warps take them
+    // one by one from a counter in shared memory, whichever warp is free.
+    __shared__ int next_task;
+    const int first = int(int64_t(BH) * blockIdx.x / gridDim.x), last = int(int64_t(BH) * (blockIdx.x + 1) / gridDim.x);
+    if (tid == 0) next_task = first + RN_DECP_THREADS / 32;
+    __syncthreads();
+
 #pragma unroll 1
-    for (int bh = blockIdx.x * (RN_DECP_THREADS / 32) + warp; bh < BH; bh += gridDim.x * (RN_DECP_THREADS / 32)) {
+    for (int bh = first + warp; bh < last;) {
+        int following = 0;
+        if (lane == 0) following = atomicAdd(&next_task, 1);
+        following = __shfl_sync(RN_FULL, following, 0);
+        const int bh_cur = bh;
+        bh = following;
+        rn_decode_pair_task<T, NV>(p, bh_cur, lane, hl, which, cand, wbuf, &mbar[warp], phase);
+        if (phase & 2u) break;  // a bulk copy never completed
+    }
+}
+
+// One (b,h) pair on one warp; phase bit 0 = parity of the warp's mbarrier, bit 1 = failure.
+template <typename T, int NV>
+__device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
+                                                    const int which, const uint32_t cand, float *wbuf, uint64_t *bar,
+                                                    uint32_t &phase) {
+    constexpr int U = 2, P = 64, K = 16;
+    constexpr int C = NV * 128;
+    constexpr uint32_t ROW_BYTES = C * 4;
+    {
         const int b = bh / p.H, h = bh % p.H;
         T *y = static_cast<T *>(p.y) + int64_t(bh) * C;
         if (p.mask != nullptr && p.mask[b] == 0) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
-            continue;
+            return;
         }
         float *slot = p.slot + int64_t(bh) * p.A * C;
         float *mass = p.mass + int64_t(bh) * p.A;
@@ -468,9 +499,9 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
         const float mass_l = live_w ? mass[a_l] : 0.f;  // requested before the row traffic
         const int nlive = __popc(__ballot_sync(RN_FULL, live_w));
         if (nlive > 0) {
-            if (lane == 0) rn_mbar_expect_tx(&mbar[warp], uint32_t(nlive) * ROW_BYTES);
+            if (lane == 0) rn_mbar_expect_tx(bar, uint32_t(nlive) * ROW_BYTES);
             __syncwarp();
-            if (live_w) rn_bulk_g2s(wbuf + lane * C, slot + int64_t(a_l) * C, ROW_BYTES, &mbar[warp]);
+            if (live_w) rn_bulk_g2s(wbuf + lane * C, slot + int64_t(a_l) * C, ROW_BYTES, bar);
         }
 
         // ---- read rows: per-lane loads into registers, in flight together with the bulk copies -------------
@@ -500,7 +531,7 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
 
         bool landed = true;
         if (nlive > 0) {
-            landed = rn_mbar_wait_bounded(&mbar[warp], phase);
+            landed = rn_mbar_wait_bounded(bar, phase & 1u);
             phase ^= 1u;
         }
         if (!__all_sync(RN_FULL, landed)) {
@@ -508,7 +539,8 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
             // and stop using the buffer (the copy may still land)
 #pragma unroll
             for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(NAN, NAN, NAN, NAN));
-            break;
+            phase |= 2u;
+            return;
         }
 #pragma unroll
         for (int k = 0; k < K; ++k) {
