@@ -285,10 +285,10 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
         return sum(v) / max(len(v), 1)
 
     per_bh = T * (C * 2 + C * 2) + 2 * A * C * 4  # apply kernel: x once, y once, slot state in and out
-    # DRAM traffic of the apply kernel from the ncu capture of the small case (B2 T4096 H16: 143.9 MB read
-    # + 68.3 MB written, profiles/rn_gsu_apply_fast_kernel_prefill_small.md), per (b,t,h); it grows in
+    # DRAM traffic of the apply kernel from the ncu capture of the small case (B2 T4096 H16: 139.4 MB read
+    # + 65.7 MB written, profiles/rn_gsu_apply_fast_kernel_prefill_small.md), per (b,t,h); it grows in
     # proportion to the units processed (event records and x/y rows per token-head)
-    traffic = (143.941888e6 + 68.328704e6) / (2 * 4096 * 16) * (B * T * H)
+    traffic = (139.350016e6 + 65.725184e6) / (2 * 4096 * 16) * (B * T * H)
     step_bytes = B * H * (T * (2 * U * P * 2 + C * 2 + 2 + C * 2) + 2 * A * C * 4 + 2 * A * 4)
     return dict(
         tokens_per_step=B * T, ms_total=ms, steps=args.steps, e2e_ms_total=e2e_ms, e2e_steps=e2e_steps,
@@ -561,8 +561,11 @@ def main():
                                "algorithmic_bytes": bwd_bytes, "frac": bwd_bytes / (bw["total_ms"] / 1e3) / 1e9 / peak}
     if extra:
         d, a = extra["decode"], extra["addr"]
+        # achieved bandwidth from the graph-replayed step time (kernel plus position increment, back to back);
+        # kernel_ms is the same kernel bracketed by events in eager mode, event overhead included
+        dec_gbs = d["bytes_per_step"] / (d["ms_per_step"] / 1e3) / 1e9
         line["decode"] = {"tokens_per_s": world * d["tokens_per_s"], "ms_per_step": d["ms_per_step"], "kernel_ms": d["kernel_ms"],
-                          "achieved_gbs": d["kernel_gbs"], "frac": None if d["kernel_gbs"] is None else d["kernel_gbs"] / peak,
+                          "achieved_gbs": dec_gbs, "frac": dec_gbs / peak, "timing": "cuda_graph_replay",
                           "algorithmic_bytes_per_step": d["bytes_per_step"], "steps": d["steps"],
                           "workload": "decode B256 H16 U2 P64 K16 C128, fp32 state 8.6 GB"}
         line["addr"] = {"tokens_per_s": world * a["tokens_per_s"], "kernel_ms": a["kernel_ms"], "achieved_gbs": a["kernel_gbs"],

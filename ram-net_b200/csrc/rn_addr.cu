@@ -326,10 +326,13 @@ extern "C" int rn_addr_bwd(const int32_t *idx, const float *val, const int64_t *
     RnDeviceGuard guard(device);
     RN_REQUIRE(guard.ok, "cannot make device %d current", device);
 
+    rn_prof_reset();
+    rn_prof_mark(cudaStream_t(stream));
     if (rn_addr_bwd_fast(idx, val, out_strides, d_val, dval_strides, w_addr, r_addr, dtype, addr_strides, pos, pos_strides,
                          d_w, d_r, dgrad_strides, B, H, U, P, T, E, A, Kw, Kr, w_re_norm, r_re_norm, w_neg, r_neg,
                          cudaStream_t(stream)) == 0) {
         RN_CUDA(cudaGetLastError());
+        rn_prof_mark(cudaStream_t(stream));
         return 0;
     }
 
@@ -358,5 +361,6 @@ extern "C" int rn_addr_bwd(const int32_t *idx, const float *val, const int64_t *
     else if (dtype == RN_F16) rn_launch_addr_bwd<__half>(p, ppl, grid, cudaStream_t(stream));
     else rn_launch_addr_bwd<__nv_bfloat16>(p, ppl, grid, cudaStream_t(stream));
     RN_CUDA(cudaGetLastError());
+    rn_prof_mark(cudaStream_t(stream));
     return 0;
 }

@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     __shared__ float gam[2][RN_GSU_LMAX];
     __shared__ float tok_scale[RN_GSU_LMAX];
     __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
-    __shared__ int n_heads;
+    __shared__ int n_heads, n_rheads;
 
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
@@ -23,11 +23,12 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     const int A = p.A, KT = p.Kw + p.Kr, NEp = p.NEp;
     const bool pow2 = (A & (A - 1)) == 0;
 
-    // dynamic smem: [mass A][claim A][nxt NEp][last A] (SMEM_TABLES) | ev_v[NE] ev_c[NE] (mass-aware only)
+    // dynamic smem: [mass A][claim A][nxt NEp][prv NEp][last A][clen A] (SMEM_TABLES) | ev_v[NE] ev_c[NE] (mass-aware only)
     unsigned char *cur = dyn;
     float *mass;
     uint32_t *claim;
-    uint16_t *nxt = nullptr, *last = nullptr;  // successor of every event on its slot; latest event of every slot
+    // successor / predecessor of every event on its slot; latest event of every slot; its events after the first
+    uint16_t *nxt = nullptr, *prv = nullptr, *last = nullptr, *clen = nullptr;
     if (SMEM_TABLES) {
         mass = reinterpret_cast<float *>(cur);
         cur += size_t(A) * 4;
@@ -35,7 +36,11 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         cur += size_t(A) * 4;
         nxt = reinterpret_cast<uint16_t *>(cur);
         cur += size_t(NEp) * 2;
+        prv = reinterpret_cast<uint16_t *>(cur);
+        cur += size_t(NEp) * 2;
         last = reinterpret_cast<uint16_t *>(cur);
+        cur += (size_t(A) * 2 + 15) / 16 * 16;
+        clen = reinterpret_cast<uint16_t *>(cur);
         cur += (size_t(A) * 2 + 15) / 16 * 16;
     } else {
         mass = p.mass_out + int64_t(bh) * A;
@@ -99,7 +104,10 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         float ev[EPT], ec[EPT], em[EPT];  // slot, weight, coefficient, mass before the write
         int er[EPT];          // round, or -1 dead (zero weight / masked token), -3 out of range
         uint32_t pend = 0;
-        if (tid == 0) n_heads = 0;
+        if (tid == 0) {
+            n_heads = 0;
+            n_rheads = 0;
+        }
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             er[j] = -3;
@@ -112,7 +120,10 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 er[j] = live ? 0 : -1;
                 if (live) pend |= 1u << j;
             }
-            if (SMEM_TABLES && j * NT + tid < NEp) nxt[j * NT + tid] = 0xffffu;
+            if (SMEM_TABLES && j * NT + tid < NEp) {
+                nxt[j * NT + tid] = 0xffffu;
+                prv[j * NT + tid] = 0xffffu;
+            }
         }
         prefetch(chunk + 1);
 
@@ -137,8 +148,12 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                         ec[j] = p.mass_aware ? ev[j] * em[j] : ev[j];
                     }
                     if (SMEM_TABLES) {  // link the slot's events in time order (one winner per slot and round)
-                        if (R > 0) nxt[last[ea[j]]] = uint16_t(j * NT + tid);
+                        if (R > 0) {
+                            nxt[last[ea[j]]] = uint16_t(j * NT + tid);
+                            prv[j * NT + tid] = last[ea[j]];
+                        }
                         last[ea[j]] = uint16_t(j * NT + tid);
+                        clen[ea[j]] = uint16_t(R);  // ends as the round of the slot's last event
                     }
                     er[j] = R;
                     claim[ea[j]] = 0xffffffffu;
@@ -213,8 +228,45 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 if (p.wide) o_slot[e] = ea[j];
             }
         }
-        __syncthreads();  // n_heads is complete
-        if (tid == 0) o_heads[0] = uint16_t(n_heads);
+        // ---- the mirror image for a sweep against time --------------------------------------------------
+        if (SMEM_TABLES && p.reverse) {
+            uint2 *o_rpair = reinterpret_cast<uint2 *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 17 + 16);
+            uint16_t *o_rheads = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 25 + 16);
+            int back[EPT];  // events of the slot after this one
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                back[j] = er[j] >= 0 ? int(clen[ea[j]]) - er[j] : -1;
+                const bool emit = back[j] == 1;
+                const unsigned act = __ballot_sync(RN_FULL, emit);
+                if (act != 0u) {
+                    const int lane = tid & 31, leader = __ffs(act) - 1;
+                    int base = 0;
+                    if (lane == leader) base = atomicAdd(&n_rheads, __popc(act));
+                    base = __shfl_sync(RN_FULL, base, leader);
+                    if (emit) o_rheads[8 + base + __popc(act & ((1u << lane) - 1u))] = uint16_t(j * NT + tid);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                const int e = j * NT + tid;
+                if (e < NEp) {
+                    uint32_t link = RN_LINK_DEAD;
+                    if (er[j] >= 0) {
+                        const uint32_t kind = back[j] == 0 ? RN_KIND_FIRST : (back[j] == 1 ? RN_KIND_HEAD : RN_KIND_LATER);
+                        link = (ea[j] & 0xffffu) | (kind << RN_LINK_KIND_SHIFT);
+                        const uint32_t pv = prv[e];
+                        if (pv != 0xffffu) link |= RN_LINK_NEXT | (pv << 16);
+                    }
+                    o_rpair[e] = make_uint2(__float_as_uint(er[j] >= 0 ? ec[j] : 0.f), link);
+                }
+            }
+        }
+        __syncthreads();  // n_heads / n_rheads are complete
+        if (tid == 0) {
+            o_heads[0] = uint16_t(n_heads);
+            if (SMEM_TABLES && p.reverse)
+                reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 25 + 16)[0] = uint16_t(n_rheads);
+        }
         if (p.prev_mass != nullptr) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j)
@@ -618,7 +670,7 @@ static int rn_fast_geometry(int threads, int L, int KT, int cs, int *tpt_log2) {
 }
 
 int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device,
-                       RnGsuPlan *pl) {
+                       RnGsuPlan *pl, int reverse) {
     RN_REQUIRE(B > 0 && H > 0 && T > 0 && A > 0 && C > 0, "prefill dims must be positive");
     RN_REQUIRE(Kw > 0 && Kw <= 128 && Kr > 0 && Kr <= 128, "Expect 0 < top_k <= 128 (got %lld, %lld)", (long long)Kw,
                (long long)Kr);
@@ -634,12 +686,14 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
     pl->sched_ept = pl->NE > 2 * RN_SCHED_THREADS_MAX ? 4 : 2;
     pl->sched_threads = int(rn_align((pl->NE + pl->sched_ept - 1) / pl->sched_ept, 32));
     const size_t ev_bytes = size_t(pl->NE) * 8 + 16;  // mass-aware per-event scratch
-    // mass + claim tables, the successor links of a chunk's events and the latest event of every slot
-    const size_t table_bytes = size_t(A) * 8 + size_t(pl->NEp) * 2 + rn_align(size_t(A) * 2, 16);
+    // mass + claim tables, the successor / predecessor links of a chunk's events, the latest event and the
+    // number of later events of every slot
+    const size_t table_bytes = size_t(A) * 8 + size_t(pl->NEp) * 4 + 2 * rn_align(size_t(A) * 2, 16);
     pl->smem_tables = (table_bytes + ev_bytes) <= RN_SMEM_BUDGET;
     pl->sched_smem = rn_align((pl->smem_tables ? table_bytes : 0) + ev_bytes, 16);
     pl->wide = A > 65536;
-    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 21 : 17) + 16, 128));
+    pl->reverse = reverse && !pl->wide;
+    pl->rec_bytes = int64_t(rn_align(RN_GSU_HDR_BYTES + size_t(pl->NEp) * (pl->wide ? 21 : (pl->reverse ? 26 : 17)) + 32, 128));
 
     // apply kernel: channels per CTA.  Largest slice that still gives two CTAs per SM of work,
     // else the smallest one (most parallelism).

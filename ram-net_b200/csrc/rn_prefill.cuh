@@ -30,6 +30,12 @@
 //                   memory)
 //   u16 heads[8 + NEp/2]:  heads[0] = number of chains, heads[8..] their head events in any order
 //   u32 slot[NEp]:  only in the wide format (A > 65536)
+// Records built for a backward pass (narrow format only) continue with the mirror image for the sweep
+// that runs against time:
+//   {f32 coef, u32 link}[NEp]:  link with the PRECEDING event of the slot instead of the following one and
+//                   kind 0 = last event of its slot in the chunk, 2 = second to last (head of the backward
+//                   chain), 3 = earlier
+//   u16 heads[8 + NEp/2]:  the backward chain heads
 // The first events (~80 % of a chunk) are applied token-major (dense).  The later events of a slot
 // form a chain (head, then link by link); the fast apply kernel walks a chain with the slot row in
 // registers.  The backward sweeps and the general apply kernel go round by round over meta[]
@@ -86,6 +92,7 @@ struct RnGsuParams {
     uint32_t *claim;          // global claim table (B*H*A) when the tables do not fit shared memory
     float *prev_mass;         // optional: mass of the slot before each write, [(bh*T + t)*Kw + k] (backward)
     float *read_mass;         // optional: mass of the slot at each read, [(bh*T + t)*Kr + k] (mass-aware backward)
+    int reverse;              // also emit the backward pairs / heads of every chunk
     // apply kernel
     int cs;                   // channels per CTA (multiple of 4)
     int nslices;
@@ -108,6 +115,7 @@ struct RnGsuPlan {
     size_t sched_smem;
     int wide;              // A > 65536: records carry a separate slot array
     int64_t rec_bytes;
+    int reverse;           // records carry the backward links
     int fast;              // fast apply kernel (C % 4 == 0, narrow records, state in shared memory)
     int tpt_log2, ev;      // fast apply kernel: threads per token, events per thread
     int tptb_log2, evb;    // backward sweep kernels (RN_SWEEP_THREADS threads)
@@ -117,7 +125,9 @@ struct RnGsuPlan {
     size_t off_records, off_claim, total;
 };
 
-int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device, RnGsuPlan *pl);
+// reverse: the records also carry the backward links (see above); used by the backward entry points
+int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int device, RnGsuPlan *pl,
+                int reverse = 0);
 int rn_gsu_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, int dtype, cudaStream_t stream);
 inline size_t rn_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

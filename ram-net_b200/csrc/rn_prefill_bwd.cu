@@ -38,10 +38,20 @@ __device__ __forceinline__ float rn_group_sum(float v, int G, unsigned mask) {
 }
 
 // ------------------------------------------------------------------------------------------
-// replay / reverse kernels (token-major, see rn_gsu_apply_fast_kernel)
+// replay / reverse kernels: same organisation as rn_gsu_apply_fast_kernel
 // ------------------------------------------------------------------------------------------
+// One 1024-thread CTA per (b,h, channel slice); the slice of the slot state (replay) or of its gradient
+// (reverse) stays in shared memory; the {coef, link} pairs and the chain heads of a chunk arrive by a
+// 1-D bulk async copy one chunk ahead (one polling thread).  An event that is the first (replay) / the
+// last (reverse) of its slot in the chunk is handled token-major, two events in flight per thread; the
+// other events of a slot form a chain that one thread group walks with the row in registers, forwards
+// in time in the replay and against it in the reverse sweep.
+//   replay   write: delta = x - slot is stored for the reverse sweep, slot += gain * delta
+//            read:  d_r += <slot, d_y>   (float atomics across the channel slices)
+//   reverse  read:  d_slot += r * d_y
+//            write: d_gain += <d_slot, delta>, d_x += gain * d_slot, d_slot *= 1 - gain
 template <typename T, int CS, int EV, bool REVERSE>
-__global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2) {
+__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2) {
     constexpr int G = CS / 4;
     const RnGsuParams &p = bp.f;
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -54,7 +64,8 @@ __global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     const int C = p.C, A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, L = p.L;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);
-    const uint32_t rec_copy = uint32_t(RN_GSU_HDR_BYTES + size_t(p.NEp) * 8);
+    const uint32_t rec_copy = uint32_t(size_t(p.NEp) * 9 + 16);  // {coef, link}[NEp], heads[8 + NEp/2]
+    const uint32_t kt_magic = 0xffffffffu / uint32_t(KT) + 1u;  // e / KT == __umulhi(e, kt_magic) for e < 4096
 
     const int TPT = 1 << tpt_log2;
     const int KL = TPT / G;
@@ -62,11 +73,15 @@ __global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     const int w = tid & (TPT - 1);
     const int sub = w % G, q = w / G;
     const bool chan_ok = sub * 4 < cvalid;
-    const unsigned gmask = (G >= 32 ? 0xffffffffu : ((1u << G) - 1u)) << (lane & ~(G - 1));
+    const unsigned gmask = (G >= 32 ? 0xffffffffu : ((1u << G) - 1u)) << (lane & ~(G - 1));  // the lanes of one event
 
+    // dynamic smem: rec[2][rec_stride] | S[A*CS] | xt[L*CS] (replay) | dyt[L*CS] | dxlate[L*Kw*CS] (reverse)
     const size_t rec_stride = (size_t(rec_copy) + 127) / 128 * 128;
     unsigned char *rec0 = dyn;
     float *S = reinterpret_cast<float *>(dyn + 2 * rec_stride);  // slot slice (replay) or d_slot slice (reverse)
+    float *xt = S + size_t(A) * CS;
+    float *dyt = xt + size_t(L) * CS;
+    float *dxlate = dyt + size_t(L) * CS;
 
     if (tid == 0) {
         rn_mbar_init(&mbar[0], 1);
@@ -74,16 +89,22 @@ __global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
         rn_mbar_fence_init();
     }
     __syncthreads();
-    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes;
+    // forward sweeps read the pairs / heads built for time order, the reverse sweep their mirror image
+    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes + RN_GSU_HDR_BYTES +
+                                   size_t(p.NEp) * (REVERSE ? 17 : 8) + (REVERSE ? 16 : 0);
     const int first = REVERSE ? p.nchunks - 1 : 0;
     const int step = REVERSE ? -1 : 1;
-    if (tid == 0) {
-        rn_mbar_expect_tx(&mbar[0], rec_copy);
-        rn_bulk_g2s(rec0, records + int64_t(first) * p.rec_bytes, rec_copy, &mbar[0]);
-    }
+    auto fetch = [&](int it, int chunk) {  // one thread; the target buffer was last read before a CTA barrier
+        uint64_t *bar = &mbar[it & 1];
+        rn_mbar_expect_tx(bar, rec_copy);
+        rn_bulk_g2s(rec0 + (it & 1) * rec_stride, records + int64_t(chunk) * p.rec_bytes, rec_copy, bar);
+    };
+    auto landed = [&](int it) { return rn_mbar_wait_bounded(&mbar[it & 1], uint32_t(it >> 1) & 1u); };
+    bool failed = false;
+    if (tid == 0) fetch(0, first);
     {
         const float *src = (REVERSE ? bp.dslot_post : p.slot_in) + int64_t(bh) * A * C + c0;
-        for (int i = tid; i < A * G; i += RN_SWEEP_THREADS) {
+        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
             const int a = i / G, sg = i - a * G;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (sg * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sg * 4);
@@ -94,121 +115,197 @@ __global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     const T *dy = static_cast<const T *>(bp.dy) + b * bp.dyb + h * bp.dyh + c0 + sub * 4;
     T *dx = static_cast<T *>(bp.dx) + b * bp.dxb + h * bp.dxh + c0 + sub * 4;
 
-    auto load_row = [&](const T *base, int64_t tstride, int chunk) {
+    auto load_row = [&](const T *base, int64_t tstride, int chunk) {  // raw bits, converted one chunk later
         const int t = chunk * L + tok;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (chunk >= 0 && chunk < p.nchunks && tok < L && t < p.T && chan_ok) v = rn_load4<T>(base + int64_t(t) * tstride);
+        RnRaw4<T> v = rn_zero_raw4<T>();
+        if (chunk >= 0 && chunk < p.nchunks && tok < L && t < p.T && chan_ok) v = rn_load_raw4<T>(base + int64_t(t) * tstride);
         return v;
     };
-    float4 xnext = load_row(x, p.xt, first);
-    float4 dynext = load_row(dy, bp.dyt, first);
-    __syncthreads();
+    RnRaw4<T> xnext = rn_zero_raw4<T>();
+    if (!REVERSE) xnext = load_row(x, p.xt, first);
+    RnRaw4<T> dynext = load_row(dy, bp.dyt, first);
+    if (tid == 0 && !landed(0)) failed = true;
+    if (__syncthreads_or(failed)) {
+        if (tid == 0) atomicExch(p.status, 1);
+        return;
+    }
 
-    bool failed = false;
     for (int it = 0; it < p.nchunks; ++it) {
         const int chunk = first + it * step;
-        const int buf = it & 1;
         const int t0 = chunk * L;
-        const int Lc = min(L, p.T - t0);
+        const bool tok_ok = tok < min(L, p.T - t0);
         const bool more = it + 1 < p.nchunks;
-        const float4 xv = xnext, dyv = dynext;
-        if (more && tid == 0) {
-            rn_fence_proxy_async();
-            rn_mbar_expect_tx(&mbar[buf ^ 1], rec_copy);
-            rn_bulk_g2s(rec0 + (buf ^ 1) * rec_stride, records + int64_t(chunk + step) * p.rec_bytes, rec_copy,
-                        &mbar[buf ^ 1]);
-        }
-        xnext = load_row(x, p.xt, more ? chunk + step : -1);
+        const float4 xv = rn_cvt_raw4(xnext), dyv = rn_cvt_raw4(dynext);
+        if (tid == 0 && more) fetch(it + 1, chunk + step);
+        if (!REVERSE) xnext = load_row(x, p.xt, more ? chunk + step : -1);
         dynext = load_row(dy, bp.dyt, more ? chunk + step : -1);
-        if (!rn_mbar_wait_bounded(&mbar[buf], (it >> 1) & 1)) failed = true;
-        if (__syncthreads_or(failed)) {
-            if (tid == 0) atomicExch(p.status, 1);
-            if (more) rn_mbar_wait_bounded(&mbar[buf ^ 1], ((it + 1) >> 1) & 1);
-            return;
-        }
-
-        const unsigned char *rec = rec0 + buf * rec_stride;
-        const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
-        const float *e_coef = reinterpret_cast<const float *>(rec + RN_GSU_HDR_BYTES + size_t(p.NEp) * 4);
-        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
-
-        uint32_t m[EV];
-        float cf[EV];
-        const bool tok_ok = tok < Lc;
-#pragma unroll
-        for (int j = 0; j < EV; ++j) {
-            const int k = q + j * KL;
-            m[j] = RN_EV_DEAD;
-            cf[j] = 0.f;
-            if (tok_ok && k < KT) {
-                m[j] = e_meta[tok * KT + k];
-                cf[j] = e_coef[tok * KT + k];
-            }
-        }
+        const unsigned char *rec = rec0 + (it & 1) * rec_stride;
+        const uint2 *e_pair = reinterpret_cast<const uint2 *>(rec);
+        const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(p.NEp) * 8);
         // per-write-event rows in the workspaces: index of (t, k) = (bh*T + t)*Kw + k
-        const int64_t wbase = (int64_t(bh) * p.T + t0 + tok) * Kw;
+        const int64_t wchunk = (int64_t(bh) * p.T + t0) * Kw;
+        const int64_t wbase = wchunk + int64_t(tok) * Kw;
 
-        if (!REVERSE) {
-            for (int r = 0; r < R; ++r) {
+        if (q == 0 && tok < L) {
+            if (!REVERSE) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
+            *reinterpret_cast<float4 *>(dyt + tok * CS + sub * 4) = dyv;
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // reverse: d_x of this token
+        uint32_t late = 0;                             // reverse: this thread's writes that a chain handles
+
+        // ---- token-major events: records, then rows (and deltas), then arithmetic, then stores --------------
+        constexpr int NB = EV < 2 ? EV : 2;
 #pragma unroll
-                for (int j = 0; j < EV; ++j) {
-                    if (((m[j] >> 16) & 0x1ffu) != uint32_t(r)) continue;
-                    const int k = q + j * KL;
-                    float *row = S + (m[j] & 0xffffu) * CS + sub * 4;
-                    float4 s = *reinterpret_cast<float4 *>(row);
+        for (int jb = 0; jb < EV; jb += NB) {
+            uint2 pr[NB];
+            float4 row[NB], dl[NB];
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                const int k = q + (jb + i) * KL;
+                pr[i] = make_uint2(0u, RN_LINK_DEAD);
+                if (tok_ok && k < KT) pr[i] = e_pair[tok * KT + k];
+            }
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                const int k = q + (jb + i) * KL;
+                const uint32_t kind = (pr[i].y >> RN_LINK_KIND_SHIFT) & 7u;  // bit 2: dead
+                dl[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kind < RN_KIND_HEAD) {
+                    row[i] = *reinterpret_cast<const float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4);
+                    if (REVERSE && k < Kw && chan_ok) dl[i] = *reinterpret_cast<const float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4);
+                } else if (REVERSE && kind <= RN_KIND_LATER && k < Kw) {
+                    late |= 1u << (jb + i);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                if (((pr[i].y >> RN_LINK_KIND_SHIFT) & 7u) >= RN_KIND_HEAD) continue;
+                const int k = q + (jb + i) * KL;
+                const float cf = __uint_as_float(pr[i].x);
+                float *dst = S + (pr[i].y & 0xffffu) * CS + sub * 4;
+                float4 s = row[i];
+                if (!REVERSE) {
                     if (k < Kw) {
                         const float4 d = make_float4(xv.x - s.x, xv.y - s.y, xv.z - s.z, xv.w - s.w);
                         if (chan_ok) *reinterpret_cast<float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4) = d;
-                        s.x = fmaf(cf[j], d.x, s.x);
-                        s.y = fmaf(cf[j], d.y, s.y);
-                        s.z = fmaf(cf[j], d.z, s.z);
-                        s.w = fmaf(cf[j], d.w, s.w);
-                        *reinterpret_cast<float4 *>(row) = s;
+                        s.x = fmaf(cf, d.x, s.x);
+                        s.y = fmaf(cf, d.y, s.y);
+                        s.z = fmaf(cf, d.z, s.z);
+                        s.w = fmaf(cf, d.w, s.w);
+                        *reinterpret_cast<float4 *>(dst) = s;
                     } else {
                         float dot = s.x * dyv.x + s.y * dyv.y + s.z * dyv.z + s.w * dyv.w;
                         dot = rn_group_sum(dot, G, gmask);
                         if (sub == 0) atomicAdd(bp.dval + b * bp.vb + h * bp.vh + int64_t(k) * bp.vk + int64_t(t0 + tok) * bp.vt, dot);
                     }
-                }
-                __syncthreads();
-            }
-        } else {
-            // deltas of this thread's write events, fetched before the dependent rounds
-            float4 dl[EV];
-#pragma unroll
-            for (int j = 0; j < EV; ++j) {
-                const int k = q + j * KL;
-                dl[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (k < Kw && !(m[j] & RN_EV_DEAD) && chan_ok)
-                    dl[j] = *reinterpret_cast<const float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4);
-            }
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // d_x of this token
-            for (int r = R - 1; r >= 0; --r) {
-#pragma unroll
-                for (int j = 0; j < EV; ++j) {
-                    if (((m[j] >> 16) & 0x1ffu) != uint32_t(r)) continue;
-                    const int k = q + j * KL;
-                    float *row = S + (m[j] & 0xffffu) * CS + sub * 4;
-                    float4 s = *reinterpret_cast<float4 *>(row);
+                } else {
                     if (k >= Kw) {
-                        s.x = fmaf(cf[j], dyv.x, s.x);
-                        s.y = fmaf(cf[j], dyv.y, s.y);
-                        s.z = fmaf(cf[j], dyv.z, s.z);
-                        s.w = fmaf(cf[j], dyv.w, s.w);
+                        s.x = fmaf(cf, dyv.x, s.x);
+                        s.y = fmaf(cf, dyv.y, s.y);
+                        s.z = fmaf(cf, dyv.z, s.z);
+                        s.w = fmaf(cf, dyv.w, s.w);
                     } else {
-                        float dot = s.x * dl[j].x + s.y * dl[j].y + s.z * dl[j].z + s.w * dl[j].w;
+                        float dot = s.x * dl[i].x + s.y * dl[i].y + s.z * dl[i].z + s.w * dl[i].w;
                         dot = rn_group_sum(dot, G, gmask);
                         if (sub == 0) atomicAdd(bp.dgain + wbase + k, dot);
-                        acc.x = fmaf(cf[j], s.x, acc.x);
-                        acc.y = fmaf(cf[j], s.y, acc.y);
-                        acc.z = fmaf(cf[j], s.z, acc.z);
-                        acc.w = fmaf(cf[j], s.w, acc.w);
-                        const float keep = 1.f - cf[j];
+                        acc.x = fmaf(cf, s.x, acc.x);
+                        acc.y = fmaf(cf, s.y, acc.y);
+                        acc.z = fmaf(cf, s.z, acc.z);
+                        acc.w = fmaf(cf, s.w, acc.w);
+                        const float keep = 1.f - cf;
                         s.x *= keep; s.y *= keep; s.z *= keep; s.w *= keep;
                     }
-                    *reinterpret_cast<float4 *>(row) = s;
+                    *reinterpret_cast<float4 *>(dst) = s;
                 }
-                __syncthreads();
+            }
+        }
+        __syncthreads();
+
+        // ---- the chains of this chunk, dealt to the thread groups ----------------------------------------
+        {
+            const int n_heads = heads[0];
+            const int csub = tid % G;
+            const bool cok = csub * 4 < cvalid;
+            for (int i = tid / G; i < n_heads; i += RN_APPLY_THREADS / G) {
+                int e = heads[8 + i];
+                uint2 pr = e_pair[e];
+                float *row = S + (pr.y & 0xffffu) * CS + csub * 4;
+                float4 s = *reinterpret_cast<float4 *>(row);
+                int ct = int(__umulhi(uint32_t(e), kt_magic)), ck = e - ct * KT;
+                float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (REVERSE && ck < Kw && cok) dl = *reinterpret_cast<const float4 *>(bp.delta + (wchunk + int64_t(ct) * Kw + ck) * C + c0 + csub * 4);
+                for (int guard = 0; guard < RN_GSU_NE_MAX; ++guard) {
+                    // the following event's record (and delta) is requested before this one is applied
+                    const bool more_ev = (pr.y & RN_LINK_NEXT) != 0;
+                    const int en = int((pr.y >> 16) & 0xfffu);
+                    uint2 pr_n = make_uint2(0u, 0u);
+                    int ct_n = 0, ck_n = 0;
+                    float4 dl_n = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (more_ev) {
+                        pr_n = e_pair[en];
+                        ct_n = int(__umulhi(uint32_t(en), kt_magic));
+                        ck_n = en - ct_n * KT;
+                        if (REVERSE && ck_n < Kw && cok)
+                            dl_n = *reinterpret_cast<const float4 *>(bp.delta + (wchunk + int64_t(ct_n) * Kw + ck_n) * C + c0 + csub * 4);
+                    }
+                    const float cf = __uint_as_float(pr.x);
+                    const bool wr = ck < Kw;
+                    if (!REVERSE) {
+                        if (wr) {
+                            const float4 xr = *reinterpret_cast<const float4 *>(xt + ct * CS + csub * 4);
+                            const float4 d = make_float4(xr.x - s.x, xr.y - s.y, xr.z - s.z, xr.w - s.w);
+                            if (cok) *reinterpret_cast<float4 *>(bp.delta + (wchunk + int64_t(ct) * Kw + ck) * C + c0 + csub * 4) = d;
+                            s.x = fmaf(cf, d.x, s.x);
+                            s.y = fmaf(cf, d.y, s.y);
+                            s.z = fmaf(cf, d.z, s.z);
+                            s.w = fmaf(cf, d.w, s.w);
+                        }
+                        // the lanes of a group walk the same chain, so they are converged for this shuffle
+                        const float4 dyr = *reinterpret_cast<const float4 *>(dyt + ct * CS + csub * 4);
+                        float dot = wr ? 0.f : s.x * dyr.x + s.y * dyr.y + s.z * dyr.z + s.w * dyr.w;
+                        dot = rn_group_sum(dot, G, gmask);
+                        if (!wr && csub == 0) atomicAdd(bp.dval + b * bp.vb + h * bp.vh + int64_t(ck) * bp.vk + int64_t(t0 + ct) * bp.vt, dot);
+                    } else {
+                        const float4 dyr = *reinterpret_cast<const float4 *>(dyt + ct * CS + csub * 4);
+                        float dot = wr ? s.x * dl.x + s.y * dl.y + s.z * dl.z + s.w * dl.w : 0.f;
+                        dot = rn_group_sum(dot, G, gmask);
+                        if (wr) {
+                            if (csub == 0) atomicAdd(bp.dgain + wchunk + int64_t(ct) * Kw + ck, dot);
+                            *reinterpret_cast<float4 *>(dxlate + (ct * Kw + ck) * CS + csub * 4) = make_float4(cf * s.x, cf * s.y, cf * s.z, cf * s.w);
+                            const float keep = 1.f - cf;
+                            s.x *= keep; s.y *= keep; s.z *= keep; s.w *= keep;
+                        } else {
+                            s.x = fmaf(cf, dyr.x, s.x);
+                            s.y = fmaf(cf, dyr.y, s.y);
+                            s.z = fmaf(cf, dyr.z, s.z);
+                            s.w = fmaf(cf, dyr.w, s.w);
+                        }
+                    }
+                    if (!more_ev) break;
+                    e = en;
+                    pr = pr_n;
+                    ct = ct_n;
+                    ck = ck_n;
+                    dl = dl_n;
+                }
+                *reinterpret_cast<float4 *>(row) = s;
+            }
+        }
+        // the next record (requested at the top of this step) has to be there for the next step
+        if (tid == 0 && more && !landed(it + 1)) failed = true;
+        if (__syncthreads_or(failed)) {
+            if (tid == 0) atomicExch(p.status, 1);
+            return;
+        }
+
+        if (REVERSE) {
+            // ---- d_x: the writes that a chain handled, then combine the k-lanes ----------------------------------
+#pragma unroll
+            for (int j = 0; j < EV; ++j) {
+                if (!(late & (1u << j))) continue;
+                const int k = q + j * KL;
+                const float4 v = *reinterpret_cast<const float4 *>(dxlate + (tok * Kw + k) * CS + sub * 4);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
             }
             for (int off = G; off < TPT; off <<= 1) {
                 acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
@@ -223,7 +320,7 @@ __global__ void __launch_bounds__(RN_SWEEP_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     if (REVERSE) {
         __syncthreads();
         float *dst = bp.dslot_out + int64_t(bh) * A * C + c0;
-        for (int i = tid; i < A * G; i += RN_SWEEP_THREADS) {
+        for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
             const int a = i / G, sg = i - a * G;
             if (sg * 4 < cvalid)
                 *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sg * 4);
@@ -413,7 +510,7 @@ extern "C" int64_t rn_gsu_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, i
                                               int device) {
     rn_clear_error();
     RnGsuPlan pl;
-    if (rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return -1;
+    if (rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl, 1)) return -1;
     RnBwdLayout lo;
     rn_bwd_layout(pl, B, H, T, C, Kw, Kr, &lo);
     return int64_t(lo.total);
@@ -422,18 +519,25 @@ extern "C" int64_t rn_gsu_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, i
 template <typename T, bool REVERSE>
 static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaStream_t stream) {
     const int grid = bp.f.B * bp.f.H * pl.nslices;
+    // records double buffered, state slice, x / d_y rows of the chunk, per-(token,k) d_x buffer of the reverse chains
+    const size_t smem = 2 * rn_align(size_t(pl.NEp) * 9 + 16, 128) +
+                        (size_t(bp.f.A) * pl.cs + 2 * size_t(pl.L) * pl.cs + (REVERSE ? size_t(pl.L) * bp.f.Kw * pl.cs : 0)) * 4;
+    if (smem > 227 * 1024) {
+        rn_set_error("backward sweep needs %zu bytes of shared memory", smem);
+        return 1;
+    }
 #define RN_CASE(CSV, EVV)                                                                                            \
-    if (pl.cs == CSV && pl.evb == EVV) {                                                                              \
+    if (pl.cs == CSV && pl.ev == EVV) {                                                                               \
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE>,                                  \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, int(pl.apply_smem)));              \
-        rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE><<<grid, RN_SWEEP_THREADS, pl.apply_smem, stream>>>(bp, pl.tptb_log2); \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));                       \
+        rn_gsu_bwd_sweep_kernel<T, CSV, EVV, REVERSE><<<grid, RN_APPLY_THREADS, smem, stream>>>(bp, pl.tpt_log2);    \
         return 0;                                                                                                    \
     }
 #define RN_CASES(CSV) RN_CASE(CSV, 1) RN_CASE(CSV, 2) RN_CASE(CSV, 4) RN_CASE(CSV, 8) RN_CASE(CSV, 16)
     RN_CASES(4) RN_CASES(8) RN_CASES(16) RN_CASES(32)
 #undef RN_CASES
 #undef RN_CASE
-    rn_set_error("no backward kernel for %d channels per CTA, %d events per thread", pl.cs, pl.evb);
+    rn_set_error("no backward kernel for %d channels per CTA, %d events per thread", pl.cs, pl.ev);
     return 1;
 }
 
@@ -498,7 +602,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     RN_REQUIRE(dtype == RN_F32 || dtype == RN_F16 || dtype == RN_BF16, "unsupported dtype code %d", dtype);
     RN_REQUIRE(x_strides[3] == 1 && dy_strides[3] == 1 && dx_strides[3] == 1, "Tensor x / d_y / d_x last dim must be contiguous");
     RnGsuPlan pl;
-    if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return rc;
+    if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl, 1)) return rc;
     RN_REQUIRE(pl.fast, "the backward pass needs C %% 4 == 0, A <= 65536 and a channel slice of the state that fits shared "
                         "memory (A=%lld, C=%lld)", (long long)A, (long long)C);
     const size_t esz = dtype == RN_F32 ? 4 : 2;
@@ -536,6 +640,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     p.wide = pl.wide;
     p.claim = reinterpret_cast<uint32_t *>(fws + pl.off_claim);
     p.cs = pl.cs; p.nslices = pl.nslices; p.state_in_smem = pl.state_in_smem;
+    p.reverse = 1;
     p.prev_mass = reinterpret_cast<float *>(ws + lo.off_prev_mass);
     p.read_mass = mass_aware ? reinterpret_cast<float *>(ws + lo.off_read_mass) : nullptr;
     // the schedule kernel writes the final mass somewhere: d_mass doubles as that scratch before
