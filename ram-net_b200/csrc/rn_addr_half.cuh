@@ -33,43 +33,64 @@ __device__ __forceinline__ uint64_t shfl_idx(uint64_t k, int src) {
     const uint32_t hi = __shfl_sync(RN_FULL, uint32_t(k >> 32), src), lo = __shfl_sync(RN_FULL, uint32_t(k), src);
     return (uint64_t(hi) << 32) | lo;
 }
-// afterwards (a, b) descending if desc, ascending otherwise
-template <typename Key>
-__device__ __forceinline__ void cmpx_dir(Key &a, Key &b, bool desc) {
-    const bool swap = (a < b) == desc;
-    const Key t = swap ? b : a;
-    b = swap ? a : b;
+// afterwards a >= b
+__device__ __forceinline__ void cmpx_desc(uint32_t &a, uint32_t &b) {
+    const uint32_t mx = max(a, b), mn = min(a, b);
+    a = mx;
+    b = mn;
+}
+__device__ __forceinline__ void cmpx_desc(uint64_t &a, uint64_t &b) {
+    const bool lt = a < b;
+    const uint64_t t = lt ? b : a;
+    b = lt ? a : b;
     a = t;
 }
 // keep the larger (or the smaller) of this lane's key and the partner's
-template <typename Key>
-__device__ __forceinline__ Key pick(Key mine, Key other, bool keep_max) {
+__device__ __forceinline__ uint32_t pick(uint32_t mine, uint32_t other, bool keep_max) {
+    return keep_max ? max(mine, other) : min(mine, other);
+}
+__device__ __forceinline__ uint64_t pick(uint64_t mine, uint64_t other, bool keep_max) {
     return ((mine < other) == keep_max) ? other : mine;
 }
 
 // Bitonic sort, descending, of the 64 keys of a half-warp; element index = lane_in_half * 4 + slot.
+// The variant whose merges start with a mirrored exchange (element i with i ^ (size - 1)): every
+// compare-exchange then points the same way (the larger key to the lower index), so the only per-lane
+// predicate is "this lane holds the lower element", one test per lane-distance bit for the whole sort.
 // Every lane of the warp must call it (the two halves sort independently).
 template <typename Key>
 __device__ __forceinline__ void sort64_desc(Key (&k)[4], const int hl) {
+    const bool low[4] = {(hl & 1) == 0, (hl & 2) == 0, (hl & 4) == 0, (hl & 8) == 0};
 #pragma unroll
-    for (int kk = 2; kk <= 64; kk <<= 1) {
+    for (int lg = 1; lg <= 6; ++lg) {  // merges of 2^lg elements
+        if (lg >= 3) {
+            // mirrored exchange with lane ^ (2^(lg-2) - 1), slots reversed
+            const int m = (1 << (lg - 2)) - 1;
+            const bool lower = low[lg - 3];  // highest bit of the lane distance
+            Key o[4];
 #pragma unroll
-        for (int j = kk >> 1; j >= 1; j >>= 1) {
-            if (j >= 4) {
-                const int m = j >> 2;                     // distance of the partner lane
-                const bool lower = (hl & m) == 0;         // this lane holds the lower element of each pair
-                const bool desc = (hl & (kk >> 2)) == 0;  // direction of this element's block
-                const bool keep_max = lower == desc;
+            for (int s = 0; s < 4; ++s) o[s] = shfl_xor(k[3 - s], m);
 #pragma unroll
-                for (int s = 0; s < 4; ++s) k[s] = pick(k[s], shfl_xor(k[s], m), keep_max);
+            for (int s = 0; s < 4; ++s) k[s] = pick(k[s], o[s], lower);
+        } else if (lg == 2) {
+            cmpx_desc(k[0], k[3]);
+            cmpx_desc(k[1], k[2]);
+        } else {
+            cmpx_desc(k[0], k[1]);
+            cmpx_desc(k[2], k[3]);
+        }
+#pragma unroll
+        for (int jl = lg - 2; jl >= 0; --jl) {  // exchanges at distance 2^jl
+            if (jl >= 2) {
+                const int m = 1 << (jl - 2);
+#pragma unroll
+                for (int s = 0; s < 4; ++s) k[s] = pick(k[s], shfl_xor(k[s], m), low[jl - 2]);
+            } else if (jl == 1) {
+                cmpx_desc(k[0], k[2]);
+                cmpx_desc(k[1], k[3]);
             } else {
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    if ((s & j) == 0) {
-                        const bool desc = kk < 4 ? ((s & kk) == 0) : ((hl & (kk >> 2)) == 0);
-                        cmpx_dir(k[s], k[s | j], desc);
-                    }
-                }
+                cmpx_desc(k[0], k[1]);
+                cmpx_desc(k[2], k[3]);
             }
         }
     }
