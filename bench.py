@@ -456,10 +456,29 @@ def run_ncu_case(name):
             idx, val = ops.topk_addr_forward(k.permute(0, 2, 3, 4, 1), q.permute(0, 2, 3, 4, 1), E, A, pos, K, K, 0.0, 0.0)
         out = float(val.abs().mean())
     torch.cuda.synchronize()
-    print(json.dumps({"ncu_case": name, "checksum": out}))
+    emit({"ncu_case": name, "checksum": out})
+
+
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line of this run, on the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
+    # Everything else that libraries write to stdout (NCCL's version banner, for one) goes to stderr, so that
+    # stdout carries the JSON line and nothing else.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -498,7 +517,7 @@ def main():
                 "config": {"workload": "prefill_fwd sample on host cores: " + base["sample"]},
                 "cpu_baseline": base,
                 "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        emit(line)
         return
 
     if not torch.cuda.is_available():
@@ -508,7 +527,6 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
@@ -575,7 +593,7 @@ def main():
         if world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
             line["cpu_baseline"] = cpu_baseline(1)
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
