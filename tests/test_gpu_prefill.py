@@ -70,6 +70,8 @@ CASES = [
     (1, 2, 3, 4, 33, 7, (8, 8), torch.float32, False, False),
     (2, 2, 2, 64, 96, 128, (16, 16), torch.bfloat16, False, False),
     (1, 2, 2, 2, 150, 5, (2, 3), torch.float32, False, True),      # 4 slots: long same-slot chains
+    (1, 2, 2, 2, 150, 8, (2, 3), torch.float32, False, True),      # the same through the specialised apply kernel
+    (2, 2, 2, 4, 200, 16, (4, 4), torch.float32, True, False),     # 16 slots, masked tokens inside the chains
     (1, 2, 4, 3, 65, 29, (4, 12), torch.float16, True, False),
     (1, 2, 5, 4, 70, 32, (128, 128), torch.float32, False, False),  # chunk length 16
     (1, 2, 3, 32, 40, 16, (8, 8), torch.bfloat16, False, True),     # A = 32768: slot state stays in global memory
