@@ -254,8 +254,7 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
     bool inactive = false;
     int stride = 1;
 
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+    auto digit = [&](const int u) __attribute__((always_inline)) {
         // ---- digit u: keys, log-sum-exp, sorted Top-K -------------------------------------------
         // three passes over the row's P logits (L1-resident after the first): max, sum of
         // exponentials, keys; nothing but the keys stays in registers
@@ -317,6 +316,16 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
             }
         }
         stride *= P;
+    };
+    if constexpr (U >= 3) {
+        // three or more digits: the loop stays rolled.  The straight-line sorting networks are long, and with
+        // the body emitted once instruction fetch stops setting the pace (10 % faster at U = 3, P = 32, K = 8;
+        // at U = 2, P = 64, K = 16 the rolled form needs more registers and is slower)
+#pragma unroll 1
+        for (int u = 0; u < U; ++u) digit(u);
+    } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) digit(u);
     }
 
     // ---- weights and stores --------------------------------------------------------------------
