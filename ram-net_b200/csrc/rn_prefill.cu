@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 uint32_t link = RN_LINK_DEAD;
                 if (!dead) {
                     const uint32_t kind = er[j] == 0 ? RN_KIND_FIRST : (er[j] == 1 ? RN_KIND_HEAD : RN_KIND_LATER);
-                    link = (ea[j] & 0xffffu) | (kind << RN_LINK_KIND_SHIFT);
+                    link = (rn_row_of_slot(ea[j], A, p.row_shift) & 0xffffu) | (kind << RN_LINK_KIND_SHIFT);
                     const uint32_t nx = SMEM_TABLES ? nxt[e] : 0xffffu;
                     if (nx != 0xffffu) link |= RN_LINK_NEXT | (nx << 16);
                 }
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                     uint32_t link = RN_LINK_DEAD;
                     if (er[j] >= 0) {
                         const uint32_t kind = back[j] == 0 ? RN_KIND_FIRST : (back[j] == 1 ? RN_KIND_HEAD : RN_KIND_LATER);
-                        link = (ea[j] & 0xffffu) | (kind << RN_LINK_KIND_SHIFT);
+                        link = (rn_row_of_slot(ea[j], A, p.row_shift) & 0xffffu) | (kind << RN_LINK_KIND_SHIFT);
                         const uint32_t pv = prv[e];
                         if (pv != 0xffffu) link |= RN_LINK_NEXT | (pv << 16);
                     }
@@ -484,7 +484,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
             const int a = i / G, sg = i - a * G;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (sg * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sg * 4);
-            *reinterpret_cast<float4 *>(S + a * CS + sg * 4) = v;
+            *reinterpret_cast<float4 *>(S + rn_row_of_slot(uint32_t(a), A, p.row_shift) * CS + sg * 4) = v;
         }
     }
     const T *x = static_cast<const T *>(p.x) + b * p.xb + h * p.xh + c0 + sub * 4;
@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
         const int a = i / G, sg = i - a * G;
         if (sg * 4 < cvalid)
-            *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sg * 4);
+            *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + rn_row_of_slot(uint32_t(a), A, p.row_shift) * CS + sg * 4);
     }
 }
 
@@ -850,6 +850,7 @@ extern "C" int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *i
     p.slot_in = slot_in; p.slot_out = slot_out; p.mass_in = mass_in; p.mass_out = mass_out;
     p.B = int(B); p.H = int(H); p.T = int(T); p.A = int(A); p.C = int(C); p.Kw = int(Kw); p.Kr = int(Kr);
     p.L = pl.L; p.nchunks = pl.nchunks; p.NE = pl.NE; p.NEp = pl.NEp;
+    p.row_shift = rn_row_shift(A);
     p.mass_aware = mass_aware; p.eps = float(eps);
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     p.status = reinterpret_cast<int *>(ws);

@@ -22,7 +22,8 @@
 //   u32 meta[NEp]:  bits 0-15 slot (narrow format, A <= 65536), 16-23 round, 24 dead (no-op event:
 //                   zero weight or masked token)
 //   f32 coef[NEp]:  gain of a write / weight of a read (mass-aware scaling folded in)
-//   {f32 coef, u32 link}[NEp]:  the same coefficient next to the event's link word: bits 0-15 slot,
+//   {f32 coef, u32 link}[NEp]:  the same coefficient next to the event's link word: bits 0-15 row of the
+//                   slot in the shared-memory slice (rn_row_of_slot),
 //                   16-27 the following live event of the chunk on the same slot, 28-29 kind (0 first
 //                   event of its slot in the chunk, 2 second event = head of the slot's chain,
 //                   3 later), 30 dead, 31 has a
@@ -56,6 +57,23 @@ constexpr uint32_t RN_EV_DEAD = 1u << 24;
 constexpr uint32_t RN_LINK_DEAD = 1u << 30, RN_LINK_NEXT = 1u << 31;
 constexpr int RN_LINK_KIND_SHIFT = 28;
 constexpr uint32_t RN_KIND_FIRST = 0, RN_KIND_HEAD = 2, RN_KIND_LATER = 3;
+
+// Row of slot a inside a CTA's shared-memory state slice.  The Top-K addresses of a token are combinations
+// of a few best digits, so the rows that a quarter-warp touches in one access (consecutive entries of a
+// token) collide on the shared-memory bank groups more often than random rows would when rows are stored
+// in slot order.  XOR-ing the low three bits with the low bits of the upper half of the address (the next
+// digit for U = 2) sends combinations of the same few digits to different bank groups; measured on the
+// config-3 shape this beats both slot order and a hash of all address bits.  A bijection on every aligned
+// group of 8 slots (shift >= 3); the link words of a record carry this row, not the slot.
+__host__ __device__ inline uint32_t rn_row_of_slot(uint32_t a, int A, int shift) {
+    return (A & 7) ? a : a ^ ((a >> shift) & 7u);
+}
+__host__ __device__ inline int rn_row_shift(int64_t A) {
+    int bits = 0;
+    while ((int64_t(1) << (bits + 1)) <= A) ++bits;  // floor(log2(A))
+    const int s = bits / 2;
+    return s < 3 ? 3 : s;
+}
 
 __host__ __device__ inline uint32_t rn_ev_pack(uint32_t slot16, int round, bool dead) {
     return (slot16 & 0xffffu) | (uint32_t(round & 0xff) << 16) | (dead ? RN_EV_DEAD : 0u);
@@ -93,6 +111,7 @@ struct RnGsuParams {
     float *prev_mass;         // optional: mass of the slot before each write, [(bh*T + t)*Kw + k] (backward)
     float *read_mass;         // optional: mass of the slot at each read, [(bh*T + t)*Kr + k] (mass-aware backward)
     int reverse;              // also emit the backward pairs / heads of every chunk
+    int row_shift;            // rn_row_of_slot
     // apply kernel
     int cs;                   // channels per CTA (multiple of 4)
     int nslices;

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
             const int a = i / G, sg = i - a * G;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (sg * 4 < cvalid) v = *reinterpret_cast<const float4 *>(src + int64_t(a) * C + sg * 4);
-            *reinterpret_cast<float4 *>(S + a * CS + sg * 4) = v;
+            *reinterpret_cast<float4 *>(S + rn_row_of_slot(uint32_t(a), A, p.row_shift) * CS + sg * 4) = v;
         }
     }
     const T *x = static_cast<const T *>(p.x) + b * p.xb + h * p.xh + c0 + sub * 4;
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
         for (int i = tid; i < A * G; i += RN_APPLY_THREADS) {
             const int a = i / G, sg = i - a * G;
             if (sg * 4 < cvalid)
-                *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + a * CS + sg * 4);
+                *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + rn_row_of_slot(uint32_t(a), A, p.row_shift) * CS + sg * 4);
         }
     }
 }
@@ -632,6 +632,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     p.slot_in = slot_in; p.mass_in = mass_in;
     p.B = int(B); p.H = int(H); p.T = int(T); p.A = int(A); p.C = int(C); p.Kw = int(Kw); p.Kr = int(Kr);
     p.L = pl.L; p.nchunks = pl.nchunks; p.NE = pl.NE; p.NEp = pl.NEp;
+    p.row_shift = rn_row_shift(A);
     p.mass_aware = mass_aware; p.eps = float(eps);
     unsigned char *fws = ws + lo.off_fwd;
     p.status = reinterpret_cast<int *>(fws);
