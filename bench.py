@@ -286,9 +286,9 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
 
     per_bh = T * (C * 2 + C * 2) + 2 * A * C * 4  # apply kernel: x once, y once, slot state in and out
     # DRAM traffic of the apply kernel from the ncu capture of the small case (B2 T4096 H16: 139.4 MB read
-    # + 65.7 MB written, profiles/rn_gsu_apply_fast_kernel_prefill_small.md), per (b,t,h); it grows in
+    # + 69.3 MB written, profiles/rn_gsu_apply_fast_kernel_prefill_small.md), per (b,t,h); it grows in
     # proportion to the units processed (event records and x/y rows per token-head)
-    traffic = (139.350016e6 + 65.725184e6) / (2 * 4096 * 16) * (B * T * H)
+    traffic = (139.404544e6 + 69.276672e6) / (2 * 4096 * 16) * (B * T * H)
     step_bytes = B * H * (T * (2 * U * P * 2 + C * 2 + 2 + C * 2) + 2 * A * C * 4 + 2 * A * 4)
     return dict(
         tokens_per_step=B * T, ms_total=ms, steps=args.steps, e2e_ms_total=e2e_ms, e2e_steps=e2e_steps,
