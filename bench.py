@@ -187,6 +187,7 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    allocs0 = torch.cuda.memory_stats(device).get("num_device_alloc", 0)
     with ClockSampler(torch.cuda.current_device()) as clocks:
         e0.record()
         for _ in range(args.steps):
@@ -195,6 +196,8 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
         torch.cuda.synchronize()
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1))
+    # cudaMalloc calls inside the timed loop (0 when the caching allocator served every tensor from its pool)
+    device_allocs = torch.cuda.memory_stats(device).get("num_device_alloc", 0) - allocs0
     del out
 
     # end to end through the public API with pinned host inputs
@@ -296,7 +299,7 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
         kernels={"rn_addr_fast_kernel": mean(t_addr), "rn_gsu_schedule_kernel": mean(t_sched),
                  "rn_gsu_apply_fast_kernel": mean(t_apply)},
         dominant=("rn_gsu_apply_fast_kernel", B * H * per_bh, mean(t_apply)), step_bytes=step_bytes, bwd=bwd,
-        traffic=traffic,
+        traffic=traffic, device_allocs=device_allocs,
         workload="prefill_fwd B8 T16384 H16 U2 P64(A4096) Kw16 Kr16 C128 bf16, CAPE on 8 heads, zero fp32 state")
 
 
@@ -562,7 +565,7 @@ def main():
         "config": {"workload": m["workload"], "io_dtype": "bf16", "state_dtype": "f32", "per_gpu_batch": SHAPES["prefill"]["B"],
                    "l2": "inputs_exceed_l2 (1.3 GB per step)", "sharding": "batch, no data-path collective"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
-        "gpu_launches": m["launches_per_step"] * args.steps,
+        "gpu_launches": m["launches_per_step"] * args.steps, "device_allocs_in_timed_loop": m["device_allocs"],
         "clocks": m["clocks"],
         "roofline": {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind, "traffic": m["traffic"],
