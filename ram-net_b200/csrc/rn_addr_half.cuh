@@ -124,7 +124,14 @@ __device__ __forceinline__ uint32_t load_candidates(int hl) { return reinterpret
 // entry of rank hl (content index before CAPE; a no-op entry reports its rank; weight > 0, or 0 for an
 // inactive token).  cand = load_candidates(hl).  Every lane of the warp must call it.
 template <typename T>
-__device__ __forceinline__ void decode_u2p64k16(const T *src, const float rho, const int lane, const uint32_t cand,
+__device__ __forceinline__ void load_logits(const T *src, const int lane, uint2 (&raw)[2]) {
+    raw[0] = *reinterpret_cast<const uint2 *>(src + (lane & 15) * 4);
+    raw[1] = *reinterpret_cast<const uint2 *>(src + 64 + (lane & 15) * 4);
+}
+// logits: this lane's 4 + 4 logits of the two digits as loaded by load_logits (so that a caller can request
+// them ahead of time)
+template <typename T>
+__device__ __forceinline__ void decode_u2p64k16(const uint2 (&logits)[2], const float rho, const int lane, const uint32_t cand,
                                                 int &content, float &weight) {
     static_assert(!rn_fast::Raw<T>::wide, "16-bit logits only");
     constexpr float LOG2E = 1.4426950408889634f;
@@ -135,7 +142,7 @@ __device__ __forceinline__ void decode_u2p64k16(const T *src, const float rho, c
     bool inactive = false;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(src + u * 64 + hl * 4);
+        const uint2 raw = logits[u];
         const uint32_t p0 = uint32_t(hl) * 4u;
         uint32_t k[4];
         k[0] = (rn_fast::ord16_from_bf16(raw.x & 0xffffu) << 16) | (0xffffu - p0);

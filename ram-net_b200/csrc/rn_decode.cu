@@ -413,8 +413,8 @@ constexpr int RN_DECP_THREADS = 256;
 
 template <typename T, int NV>
 __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
-                                                    const int which, const uint32_t cand, float *wbuf, uint64_t *bar,
-                                                    uint32_t &phase);
+                                                    const int which, const uint32_t cand, const uint2 (&logits)[2],
+                                                    float *wbuf, uint64_t *bar, uint32_t &phase);
 
 template <typename T, int NV>
 __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(const RnDecodeParams p) {
@@ -443,23 +443,30 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
     if (tid == 0) next_task = first + RN_DECP_THREADS / 32;
     __syncthreads();
 
+    const T *logit_base = static_cast<const T *>(which ? p.r_addr : p.w_addr);
+    uint2 logits[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+    if (first + warp < last) rn_half::load_logits<T>(logit_base + int64_t(first + warp) * U * P, lane, logits);
 #pragma unroll 1
     for (int bh = first + warp; bh < last;) {
         int following = 0;
         if (lane == 0) following = atomicAdd(&next_task, 1);
         following = __shfl_sync(RN_FULL, following, 0);
-        const int bh_cur = bh;
-        bh = following;
-        rn_decode_pair_task<T, NV>(p, bh_cur, lane, hl, which, cand, wbuf, &mbar[warp], phase);
+        // the logits of the following pair are requested now and used after this pair is done
+        uint2 logits_next[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+        if (following < last) rn_half::load_logits<T>(logit_base + int64_t(following) * U * P, lane, logits_next);
+        rn_decode_pair_task<T, NV>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
         if (phase & 2u) break;  // a bulk copy never completed
+        bh = following;
+        logits[0] = logits_next[0];
+        logits[1] = logits_next[1];
     }
 }
 
 // One (b,h) pair on one warp; phase bit 0 = parity of the warp's mbarrier, bit 1 = failure.
 template <typename T, int NV>
 __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
-                                                    const int which, const uint32_t cand, float *wbuf, uint64_t *bar,
-                                                    uint32_t &phase) {
+                                                    const int which, const uint32_t cand, const uint2 (&logits)[2],
+                                                    float *wbuf, uint64_t *bar, uint32_t &phase) {
     constexpr int U = 2, P = 64, K = 16;
     constexpr int C = NV * 128;
     constexpr uint32_t ROW_BYTES = C * 4;
@@ -484,8 +491,7 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
         // ---- both addresses of the pair --------------------------------------------------------------
         int content;
         float weight;
-        rn_half::decode_u2p64k16<T>(static_cast<const T *>(which ? p.r_addr : p.w_addr) + int64_t(bh) * U * P, p.re_norm[which],
-                                    lane, cand, content, weight);
+        rn_half::decode_u2p64k16<T>(logits, p.re_norm[which], lane, cand, content, weight);
         const int my_slot = rn_cape(content, shift, p.A);
         // lanes 0-15: entry `lane` of the write address; their read entry comes from the upper half
         const int a_l = my_slot;
