@@ -548,19 +548,29 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
             phase |= 2u;
             return;
         }
+        // four rows at a time: their loads are issued before the first store (the compiler cannot reorder them
+        // itself, loads and stores go to the same buffer)
 #pragma unroll
-        for (int k = 0; k < K; ++k) {
-            const float gain = __shfl_sync(RN_FULL, gain_l, k);
-            if (live_mask & (1u << k)) {
+        for (int k0 = 0; k0 < K; k0 += 4) {
+            float4 cur[4][NV];
+            float gain[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                gain[i] = __shfl_sync(RN_FULL, gain_l, k0 + i);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) cur[i][v] = *reinterpret_cast<const float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (!(live_mask & (1u << (k0 + i)))) continue;  // not loaded: the buffer holds stale rows there
 #pragma unroll
                 for (int v = 0; v < NV; ++v) {
-                    float4 *cell = reinterpret_cast<float4 *>(wbuf + k * C + v * 128 + lane * 4);
-                    float4 s = *cell;
-                    s.x = fmaf(gain, xv[v].x - s.x, s.x);
-                    s.y = fmaf(gain, xv[v].y - s.y, s.y);
-                    s.z = fmaf(gain, xv[v].z - s.z, s.z);
-                    s.w = fmaf(gain, xv[v].w - s.w, s.w);
-                    *cell = s;
+                    float4 s = cur[i][v];
+                    s.x = fmaf(gain[i], xv[v].x - s.x, s.x);
+                    s.y = fmaf(gain[i], xv[v].y - s.y, s.y);
+                    s.z = fmaf(gain[i], xv[v].z - s.z, s.z);
+                    s.w = fmaf(gain[i], xv[v].w - s.w, s.w);
+                    *reinterpret_cast<float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4) = s;
                 }
             }
         }
