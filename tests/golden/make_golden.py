@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to a checkout of the reference project>
 
 It imports ``ramnet_ops`` from ``<ref>/packages/ramnet-ops/src`` (the CUDA extension is absent
 there, so only ``impl_backend='torch'`` is exercised), feeds it seeded inputs and stores inputs
@@ -103,7 +103,9 @@ def ram_case(ref, name, B, H, U, P, T, K, C, E, dtype, renorm, mass_aware, eps, 
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+    root = Path(sys.argv[1])
     sys.path.insert(0, str(root / "packages" / "ramnet-ops" / "src"))
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
