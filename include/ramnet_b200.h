@@ -43,6 +43,27 @@ int rn_prof_enable(int on);
 int rn_prof_read(float *ms, int n);
 
 /*
+ * Device-side failure report (the reference has no counterpart: its kernels have no waits that can
+ * run out; host-side errors there are TORCH_CHECKs, packages/ramnet-ops/csrc/torch_compat.h:19-22).
+ *
+ * The decode and prefill kernels wait on asynchronous copies with a bound of about a second.  A wait
+ * that runs out makes the kernel record a non-zero code (1 = wait timed out) in a per-device status
+ * word, leave the state of the affected (batch, head) as it was where it still can, and return; the
+ * entry point that launched it has already returned 0 by then.  The word is sticky.
+ * rn_device_status() copies it to *status after SYNCHRONISING `stream` (so call it at a point that
+ * may block, never inside a stream capture) and clears it when reset != 0.  0 means no kernel on
+ * this device has reported a failure since the last reset.
+ */
+int rn_device_status(int device, void *stream, int reset, int *status);
+
+/* Diagnostic for the mechanism above: launches one tiny kernel whose only bulk copy (256 bytes)
+ * completes while its barrier expects `extra_bytes` more, so that the bounded wait (shortened to
+ * 2^limit_log2 clock cycles) runs out exactly as it would in a product kernel; the kernel reports
+ * through the status word and returns with nothing in flight.  With extra_bytes == 0 the wait
+ * succeeds and the status word stays untouched.  No GPU fault, trap or hang is involved. */
+int rn_selftest_wait_timeout(int extra_bytes, int limit_log2, int device, void *stream);
+
+/*
  * Address decode (Product-Softmax over U digit sub-vectors + exact Top-K prefix search +
  * CAPE cyclic shift), write and read addresses in ONE launch.
  * Replaces ramnet_ops::topk_addr_forward / topk_addr_single_forward
@@ -133,6 +154,13 @@ int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const 
  */
 int64_t rn_gsu_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
                                int device);
+/* Launch plan of a prefill call of this shape (no counterpart in the reference; its launch geometry is fixed,
+ * packages/ramnet-ops/csrc/ram_attn_segment_parallel.cu:785-830).  Fills out[0..7]: fast apply kernel (1/0),
+ * channels per CTA, events per thread (forward), channel slices, chunk length, state slice in shared memory
+ * (1/0), events per thread (backward sweeps), schedule tables in shared memory (1/0).  reverse != 0 plans the
+ * backward pass.  Lets a test or benchmark prove that two shapes run the same template instances. */
+int rn_gsu_plan_info(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int reverse,
+                     int device, int32_t *out, int n);
 int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *idx_strides, const void *x,
                const int64_t *x_strides, const void *gamma, const int64_t *gamma_strides, int dtype,
                const uint8_t *mask, const int64_t *mask_strides, const float *slot_in, const float *mass_in,

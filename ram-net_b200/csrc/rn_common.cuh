@@ -50,6 +50,10 @@ struct RnDeviceGuard {
 
 int rn_sm_count(int device);
 
+// Per-device status word (see rn_api.cu): device address, or nullptr when it cannot be found.
+int *rn_status_word(int device);
+constexpr int RN_STATUS_WAIT_TIMEOUT = 1;  // a bounded wait on an asynchronous copy ran out
+
 // benchmark-only timing hooks (no-ops unless rn_prof_enable(1) was called on this thread)
 void rn_prof_reset();
 void rn_prof_mark(cudaStream_t stream);

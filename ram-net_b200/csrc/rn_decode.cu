@@ -1,12 +1,20 @@
-// Fused autoregressive decode step: one CTA per (batch, head).
+// Fused autoregressive decode step (address decode, gated update of the Kw selected slots, weighted read of
+// the Kr selected slots after the update, optional head RMSNorm + sigmoid gate).  Three kernels, picked by
+// shape in rn_decode_step:
 //
-//   warp 0 decodes the write address, warp 1 the read address (rn_addr.cuh), warps 2-3 stage x;
-//   the Kw selected slot rows are updated in place (row k -> warp k mod 4, 128-bit accesses when
-//   C is a multiple of 4), then the Kr read rows are gathered after a CTA barrier so a read
-//   of a slot written in this step sees the new value, reduced over K in a fixed order, and the
-//   optional head RMSNorm + sigmoid gate is applied before y is stored in the I/O dtype.
+//   rn_decode_pair_kernel  U = 2, P = 64, K = 16, 16-bit logits, C = 128 or 256: one WARP per (batch, head)
+//       pair, its two halves decode the write and the read address with sixteen lanes per address; the 16
+//       write rows go global -> shared -> global by 1-D bulk async copies (mbarrier, bounded wait), the 16
+//       read rows by per-lane loads in flight at the same time; a CTA's warps draw pairs from a shared counter.
+//   rn_decode_fast_kernel  (U,P,K) = (2,64,16), (3,32,8), (2,16,4) with 32-bit or 16-bit logits: one CTA per
+//       16 pairs, four lanes per address on warps 0-3, then warp w owns pairs 2w and 2w+1; rows as above.
+//   rn_decode_kernel       any U <= 8, P <= 128, K <= 128, C <= 1024: one CTA per pair, warp 0 / 1 decode the
+//       write / read address, rows updated in place (128-bit accesses when C is a multiple of 4), reads
+//       gathered after a CTA barrier and reduced over K in a fixed order.
 //
-// State offsets are 64-bit: B*H*A*C may exceed 2^31 elements.
+// A read of a slot written in the same step sees the new value.  State offsets are 64-bit: B*H*A*C may
+// exceed 2^31 elements.  A bounded wait that runs out is reported through the device's status word; slot
+// and mass of that pair stay as they were and its output is zero.
 #include "rn_addr_fast.cuh"
 #include "rn_addr_half.cuh"
 #include "rn_prefill.cuh"
@@ -29,6 +37,7 @@ struct RnDecodeParams {
     float re_norm[2];
     int mass_aware;
     float eps;
+    int *status;  // the device's status word (rn_status_word): set when a bounded wait runs out
 };
 
 template <typename T, int KPL, int PPL>
@@ -298,11 +307,11 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
             const float ww = __shfl_sync(RN_FULL, w_l, j);
             if (ww != 0.f && aw == ar_l) alias_l = j;
         }
-        float gain_l = 0.f;
+        float gain_l = 0.f, mass_new = 0.f;
         if (live_w) {
             const RnGate g = rn_gate(w_l, gamma, mass[a_l], p.eps);
             gain_l = g.gain;
-            mass[a_l] = g.mass;
+            mass_new = g.mass;
         }
         __syncwarp();
 
@@ -312,12 +321,18 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
             phase ^= 1u;
         }
         if (!__all_sync(RN_FULL, landed)) {
-            // a bulk copy never completed: leave the state alone, make the failure visible in the output,
-            // and stop using the buffer (the copy may still land)
+            // A bulk copy never completed: report it through the status word, leave slot AND mass of this
+            // pair as they were, give the pairs this warp still owns a defined (zero) output and stop using
+            // the buffer (the copy may still land).
+            if (lane == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
+            for (int rest = pp; rest < 2 && bh0 + warp * 2 + rest < BH; ++rest) {
+                T *yr = static_cast<T *>(p.y) + int64_t(bh0 + warp * 2 + rest) * C;
 #pragma unroll
-            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(NAN, NAN, NAN, NAN));
+                for (int v = 0; v < NV; ++v) rn_store4<T>(yr + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+            }
             break;
         }
+        if (live_w) mass[a_l] = mass_new;  // only once the rows are here: slot and mass move together
 #pragma unroll
         for (int k = 0; k < K; ++k) {
             const float w = __shfl_sync(RN_FULL, w_l, k);
@@ -455,7 +470,14 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
         uint2 logits_next[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
         if (following < last) rn_half::load_logits<T>(logit_base + int64_t(following) * U * P, lane, logits_next);
         rn_decode_pair_task<T, NV>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
-        if (phase & 2u) break;  // a bulk copy never completed
+        if (phase & 2u) {  // a bulk copy never completed: the pair this warp had already drawn gets a zero output
+            if (following < last) {
+                T *yr = static_cast<T *>(p.y) + int64_t(following) * (NV * 128);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) rn_store4<T>(yr + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+            }
+            break;
+        }
         bh = following;
         logits[0] = logits_next[0];
         logits[1] = logits_next[1];
@@ -524,11 +546,11 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
         const unsigned same = __match_any_sync(RN_FULL, my_slot) & live_mask;  // live write lanes with this lane's slot
         const int alias_up = same ? __ffs(same) - 1 : -1;
         const int alias_l = __shfl_down_sync(RN_FULL, alias_up, 16);
-        float gain_l = 0.f;
+        float gain_l = 0.f, mass_new = 0.f;
         if (live_w) {
             const RnGate g = rn_gate(w_l, gamma, mass_l, p.eps);
             gain_l = g.gain;
-            mass[a_l] = g.mass;
+            mass_new = g.mass;
         }
         __syncwarp();
         float4 xv[NV];
@@ -541,13 +563,16 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
             phase ^= 1u;
         }
         if (!__all_sync(RN_FULL, landed)) {
-            // a bulk copy never completed: leave the state alone, make the failure visible in the output,
-            // and stop using the buffer (the copy may still land)
+            // A bulk copy never completed: report it through the status word, leave slot AND mass of this
+            // pair as they were, give it a defined (zero) output and stop using the buffer (the copy may
+            // still land).
+            if (lane == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
 #pragma unroll
-            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(NAN, NAN, NAN, NAN));
+            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
             phase |= 2u;
             return;
         }
+        if (live_w) mass[a_l] = mass_new;  // only once the rows are here: slot and mass move together
         // four rows at a time: their loads are issued before the first store (the compiler cannot reorder them
         // itself, loads and stores go to the same buffer)
 #pragma unroll
@@ -748,6 +773,8 @@ extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void
     p.K[0] = int(Kw); p.K[1] = int(Kr);
     p.re_norm[0] = float(w_re_norm); p.re_norm[1] = float(r_re_norm);
     p.mass_aware = mass_aware; p.eps = float(eps);
+    p.status = rn_status_word(device);
+    RN_REQUIRE(p.status != nullptr, "cannot locate the status word of device %d", device);
 
     const int kpl = rn_per_lane_dec(Kw > Kr ? Kw : Kr), ppl = rn_per_lane_dec(P);
     const size_t smem = size_t(C) * (1 + RN_DEC_WARPS) * sizeof(float);

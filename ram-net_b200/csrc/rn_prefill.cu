@@ -49,8 +49,6 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     float *ev_v = reinterpret_cast<float *>(cur);
     float *ev_c = ev_v + p.NE;
 
-    if (bh == 0 && tid == 0) *p.status = 0;
-
     const float *mass_in = p.mass_in + int64_t(bh) * A;
     for (int a = tid; a < A; a += NT) {
         if (SMEM_TABLES || mass_in != mass) mass[a] = mass_in[a];
@@ -349,6 +347,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
         for (int r = 0; r < R; ++r) {
             for (int i = tid; i < ne * G; i += RN_GSU_THREADS) {
                 const int ev = i / G, sub = i - ev * G;
+                if (sub * 4 >= cvalid) continue;  // channel group beyond C in the last slice: nothing to touch
                 const uint32_t meta = e_meta[ev];
                 const int t = ev / KT, k = ev - t * KT;
                 const bool dead = (meta & RN_EV_DEAD) != 0;
@@ -500,7 +499,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     RnRaw4<T> xnext = load_x(0);
     if (tid == 0 && !landed(0)) failed = true;
     if (__syncthreads_or(failed)) {  // state and barriers are set up, the first record has landed
-        if (tid == 0) atomicExch(p.status, 1);
+        if (tid == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
         return;
     }
 
@@ -600,7 +599,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
         // the next record (requested at the top of this step) has to be there for the next step
         if (tid == 0 && has_next && !landed(chunk + 1)) failed = true;
         if (__syncthreads_or(failed)) {
-            if (tid == 0) atomicExch(p.status, 1);
+            if (tid == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
             return;
         }
 
@@ -752,6 +751,21 @@ extern "C" int64_t rn_gsu_workspace_bytes(int64_t B, int64_t H, int64_t T, int64
     return int64_t(pl.total);
 }
 
+// Which kernels a prefill call of this shape runs, for tests and benchmarks that must prove they exercise the
+// same template instances: out[0] = 1 fast apply kernel / 0 general, out[1] = channels per CTA, out[2] = events
+// per thread (forward), out[3] = channel slices, out[4] = chunk length, out[5] = state slice in shared memory,
+// out[6] = events per thread (backward sweeps), out[7] = schedule tables in shared memory.
+extern "C" int rn_gsu_plan_info(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr, int reverse,
+                                int device, int32_t *out, int n) {
+    rn_clear_error();
+    RN_REQUIRE(out != nullptr && n >= 8, "out must hold at least 8 integers");
+    RnGsuPlan pl{};
+    if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl, reverse)) return rc;
+    out[0] = pl.fast; out[1] = pl.cs; out[2] = pl.ev; out[3] = pl.nslices; out[4] = pl.L; out[5] = pl.state_in_smem;
+    out[6] = pl.evb; out[7] = pl.smem_tables;
+    return 0;
+}
+
 template <typename T, bool SMEM>
 static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int bh = p.B * p.H;
@@ -853,7 +867,8 @@ extern "C" int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *i
     p.row_shift = rn_row_shift(A);
     p.mass_aware = mass_aware; p.eps = float(eps);
     unsigned char *ws = static_cast<unsigned char *>(workspace);
-    p.status = reinterpret_cast<int *>(ws);
+    p.status = rn_status_word(device);
+    RN_REQUIRE(p.status != nullptr, "cannot locate the status word of device %d", device);
     p.records = ws + pl.off_records;
     p.rec_bytes = pl.rec_bytes;
     p.wide = pl.wide;

@@ -103,7 +103,7 @@ struct RnGsuParams {
     int mass_aware;
     float eps;
     // schedule workspace
-    int *status;              // device-side error word (0 = ok)
+    int *status;              // the device's status word (rn_status_word): set when a bounded wait runs out
     unsigned char *records;   // nchunks * B * H records of rec_bytes each
     int64_t rec_bytes;
     int wide;                 // records carry the separate u32 slot array
@@ -172,12 +172,12 @@ __device__ __forceinline__ bool rn_mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^31 clock cycles (about a second) and reports failure.
-__device__ __forceinline__ bool rn_mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+// Bounded wait: gives up after `limit` clock cycles (default 2^31, about a second) and reports failure.
+__device__ __forceinline__ bool rn_mbar_wait_bounded(uint64_t *bar, uint32_t parity, long long limit = (1ll << 31)) {
     if (rn_mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     while (!rn_mbar_try_wait(bar, parity)) {
-        if (clock64() - start > (1ll << 31)) return false;
+        if (clock64() - start > limit) return false;
     }
     return true;
 }

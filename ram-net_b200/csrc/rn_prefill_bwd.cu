@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     RnRaw4<T> dynext = load_row(dy, bp.dyt, first);
     if (tid == 0 && !landed(0)) failed = true;
     if (__syncthreads_or(failed)) {
-        if (tid == 0) atomicExch(p.status, 1);
+        if (tid == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
         return;
     }
 
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
         // the next record (requested at the top of this step) has to be there for the next step
         if (tid == 0 && more && !landed(it + 1)) failed = true;
         if (__syncthreads_or(failed)) {
-            if (tid == 0) atomicExch(p.status, 1);
+            if (tid == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
             return;
         }
 
@@ -635,7 +635,8 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     p.row_shift = rn_row_shift(A);
     p.mass_aware = mass_aware; p.eps = float(eps);
     unsigned char *fws = ws + lo.off_fwd;
-    p.status = reinterpret_cast<int *>(fws);
+    p.status = rn_status_word(device);
+    RN_REQUIRE(p.status != nullptr, "cannot locate the status word of device %d", device);
     p.records = fws + pl.off_records;
     p.rec_bytes = pl.rec_bytes;
     p.wide = pl.wide;

@@ -9,6 +9,7 @@ if the shared library is missing, importing this module raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
 import torch
@@ -40,6 +41,8 @@ lib.rn_decode_step.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _
 
 lib.rn_gsu_workspace_bytes.restype = ctypes.c_int64
 lib.rn_gsu_workspace_bytes.argtypes = [_i64] * 7 + [_i32]
+lib.rn_gsu_plan_info.restype = ctypes.c_int
+lib.rn_gsu_plan_info.argtypes = [_i64] * 7 + [_i32, _i32, ctypes.POINTER(ctypes.c_int32), _i32]
 lib.rn_gsu_fwd.restype = ctypes.c_int
 lib.rn_gsu_fwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _i64p, _i32, _ptr, _i64p, _ptr, _ptr, _ptr, _ptr, _ptr,
                            _i64p, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _f64, _i32, _ptr]
@@ -50,6 +53,10 @@ lib.rn_gsu_bwd.restype = ctypes.c_int
 lib.rn_gsu_bwd.argtypes = [_ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _i64p, _i32, _ptr, _i64p, _ptr, _ptr,
                            _ptr, _i64p, _ptr, _ptr, _ptr, _i64p, _ptr, _i64p, _ptr, _ptr, _ptr, _ptr, _i64,
                            _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _f64, _i32, _ptr]
+lib.rn_device_status.restype = ctypes.c_int
+lib.rn_device_status.argtypes = [_i32, _ptr, _i32, ctypes.POINTER(ctypes.c_int)]
+lib.rn_selftest_wait_timeout.restype = ctypes.c_int
+lib.rn_selftest_wait_timeout.argtypes = [_i32, _i32, _i32, _ptr]
 lib.rn_prof_enable.argtypes = [_i32]
 lib.rn_prof_read.argtypes = [ctypes.POINTER(ctypes.c_float), _i32]
 
@@ -63,6 +70,38 @@ def check(rc: int) -> None:
     from its TORCH_CHECKs, packages/ramnet-ops/csrc/torch_compat.h:19-22)."""
     if rc != 0:
         raise RuntimeError(lib.rn_last_error().decode())
+
+
+def device_status(device: torch.device | int | None = None, reset: bool = True) -> int:
+    """Status word of ``device`` (0 = no kernel reported a failure since the last reset).  Synchronises the
+    current stream of that device."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    out = ctypes.c_int(0)
+    check(lib.rn_device_status(index, ctypes.c_void_p(torch.cuda.current_stream(index).cuda_stream), int(reset),
+                               ctypes.byref(out)))
+    return int(out.value)
+
+
+CHECK_STATUS = os.environ.get("RAMNET_CHECK_STATUS", "0") not in ("", "0")
+
+
+def check_device(t: torch.Tensor) -> None:
+    """Debug mode (environment variable RAMNET_CHECK_STATUS=1): after a kernel launch, synchronise and turn a
+    device-side failure report into RuntimeError.  Off by default: the operators never synchronise."""
+    if CHECK_STATUS and not torch.cuda.is_current_stream_capturing():
+        code = device_status(t.device)
+        if code != 0:
+            raise RuntimeError(f"ramnet_ops kernel reported device status {code} (1 = a bounded wait on an "
+                               "asynchronous copy ran out); results of the last calls on this device are incomplete")
+
+
+def gsu_plan_info(B, H, T, A, C, Kw, Kr, reverse=False, device=0) -> dict:
+    """Launch plan of a prefill call (see rn_gsu_plan_info in include/ramnet_b200.h)."""
+    out = (ctypes.c_int32 * 8)()
+    check(lib.rn_gsu_plan_info(B, H, T, A, C, Kw, Kr, int(reverse), device, out, 8))
+    names = ("fast", "cs", "ev", "nslices", "L", "state_in_smem", "ev_bwd", "smem_tables")
+    return dict(zip(names, (int(v) for v in out)))
 
 
 def strides(t: torch.Tensor):

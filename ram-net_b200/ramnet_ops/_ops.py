@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _C
-from ._C import check, dtype_code, lib, ptr, stream_of, strides
+from ._C import check, check_device, dtype_code, lib, ptr, stream_of, strides
 
 _lib = torch.library.Library("ramnet_ops", "DEF")
 
@@ -65,6 +65,34 @@ def _require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise RuntimeError("ramnet_ops CUDA operators need CUDA tensors")
+
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(like: torch.Tensor, nbytes: int) -> torch.Tensor:
+    """Scratch for one kernel sequence on the current stream of ``like.device``.
+
+    One buffer per (device, stream) is kept and grown on demand, so steady-state calls allocate nothing (a
+    fresh gigabyte-sized block per call can make the caching allocator go back to the driver).  Calls on one
+    stream are ordered, so they may share it; every call rewrites what it later reads.  During a stream
+    capture the buffer comes from the capturing allocator instead and is not kept."""
+    nbytes = max(int(nbytes), 256)
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(nbytes, dtype=torch.uint8, device=like.device)
+    key = (like.device.index, torch.cuda.current_stream(like.device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        _WORKSPACES.pop(key, None)
+        ws = None
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=like.device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    """Drop the cached scratch buffers (they are re-created on the next call)."""
+    _WORKSPACES.clear()
 
 
 def _int32(t: torch.Tensor) -> torch.Tensor:
@@ -203,6 +231,7 @@ def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_
                              ptr(mask_u8), ptr(pos), ptr(y), ptr(norm_weight), ptr(gate_logits), float(norm_eps),
                              B, H, U, P, C, embed_num, w_top_k, r_top_k, float(w_re_norm), float(r_re_norm),
                              int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    check_device(y)
     return y
 
 
@@ -260,11 +289,12 @@ def gsu_forward_impl(addr_idx, addr_val, x, gamma, slot_in, mass_in, slot_out, m
     nbytes = lib.rn_gsu_workspace_bytes(B, H, T, A, C, w_top_k, r_top_k, x.device.index)
     if nbytes < 0:
         check(1)
-    ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=x.device)
+    ws = _workspace(x, nbytes)
     check(lib.rn_gsu_fwd(ptr(addr_idx), ptr(addr_val), strides(addr_idx), ptr(x), strides(x), ptr(gamma), strides(gamma),
                          dtype_code(x), ptr(mask_u8), None if mask_u8 is None else strides(mask_u8), ptr(slot_in),
-                         ptr(mass_in), ptr(slot_out), ptr(mass_out), ptr(y), strides(y), ptr(ws), int(nbytes), B, H, T,
+                         ptr(mass_in), ptr(slot_out), ptr(mass_out), ptr(y), strides(y), ptr(ws), ws.numel(), B, H, T,
                          A, C, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    check_device(y)
     return y
 
 
@@ -321,6 +351,7 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
                          ptr(mass_in), ptr(dy), strides(dy), ptr(d_slot_post), ptr(d_mass_post), ptr(d_val), strides(d_val),
                          ptr(d_x), strides(d_x), ptr(d_gamma), ptr(d_slot), ptr(d_mass), ptr(ws), int(nbytes), B, H, T, A,
                          C4, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    check_device(d_val)
     return d_val, d_x[..., :C], d_gamma, d_slot[..., :C], d_mass
 
 

@@ -51,6 +51,17 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     assert lib.rn_gsu_bwd_workspace_bytes(2, 4, 100, 256, 64, 4, 4, 0) > n
 
 
+def test_status_and_plan_entry_points_validate_before_touching_cuda():
+    C = _lib()
+    lib = C.lib
+    assert lib.rn_device_status(0, None, 0, None) != 0 and b"null pointer" in lib.rn_last_error()
+    assert lib.rn_selftest_wait_timeout(8, 16, 0, None) != 0 and b"multiple of 16" in lib.rn_last_error()
+    assert lib.rn_selftest_wait_timeout(16, 40, 0, None) != 0 and b"limit_log2" in lib.rn_last_error()
+    info = C.gsu_plan_info(8, 16, 16384, 4096, 128, 16, 16)
+    assert info["L"] == 64 and info["cs"] * info["nslices"] >= 128
+    assert lib.rn_gsu_plan_info(1, 1, 8, 16, 4, 2, 2, 0, 0, None, 8) != 0
+
+
 def test_cuda_backend_refuses_cpu_tensors():
     import ramnet_ops
     q = torch.randn(1, 4, 2, 2, 4)

@@ -77,6 +77,11 @@ CASES = [
     (1, 2, 3, 32, 40, 16, (8, 8), torch.bfloat16, False, True),     # A = 32768: slot state stays in global memory
     (1, 1, 2, 128, 20, 8, (5, 7), torch.float32, False, False),     # A = 16384
     (1, 2, 4, 7, 64, 65, (8, 8), torch.float32, True, True),
+    (1, 2, 2, 128, 20, 48, (4, 4), torch.float32, False, False),    # A = 16384, state in global memory, last channel slice partial
+    (1, 1, 2, 128, 20, 24, (4, 4), torch.float32, True, False),
+    (1, 1, 2, 128, 20, 12, (4, 4), torch.float32, False, True),
+    (1, 2, 3, 48, 40, 4, (4, 4), torch.float32, False, False),      # A = 110592 > 65536: wide records (separate slot array)
+    (1, 1, 2, 300 // 3, 30, 8, (3, 5), torch.bfloat16, True, False),
 ]
 
 
@@ -107,6 +112,24 @@ def test_prefill_matches_reference_golden(name):
                   float(z["eps"]))
     ref = (t(z["out_y"]).permute(0, 2, 1, 3), t(z["out_slot"]), t(z["out_mass"]))
     check(name, got, ref, mask, dtype)
+
+
+@pytest.mark.parametrize("C", [12, 24, 48])
+def test_untouched_slots_keep_their_bits_when_the_state_stays_in_global_memory(C):
+    """A >= 16384 keeps the slot state in global memory and C need not be a multiple of the channel slice: no
+    thread may touch the channels of a neighbouring slot or run past the last slot."""
+    B, H, U, P, T, K = 1, 2, 2, 128, 12, (4, 4)
+    A = P ** U
+    w, r, x, g, slot, mass, _, pos = make_case(B, H, U, P, T, C, torch.float32, 17)
+    E = 1
+    y, s, m = run_gpu(w, r, x, g, slot, mass, None, E, pos, K, (0.0, 0.0), False, 1e-6)
+    wi, _ = orc.topk_addr(w.float(), E, pos, K[0])
+    touched = torch.zeros(B * H * A, dtype=torch.bool)
+    touched[wi.reshape(-1).long()] = True
+    touched = touched.view(B, H, A)
+    assert torch.equal(s[~touched], slot[~touched]) and torch.equal(m[~touched], mass[~touched])
+    ref = orc.ram_attn(w.float(), r.float(), x.float(), g.float(), slot, mass, None, E, pos, K, (0.0, 0.0), False, 1e-6)
+    check("global-state", (y, s, m), ref, None, torch.float32)
 
 
 def test_inplace_equals_functional_and_chunked_calls_carry_state():

@@ -26,7 +26,7 @@ def _lib():
     return C, lib
 
 
-def _case(seed, B, H, T, A, C, Kw, Kr, dev):
+def _case(seed, B, H, T, A, C, Kw, Kr, dev, dtype=torch.float32):
     g = torch.Generator(device=dev).manual_seed(seed)
     KT = Kw + Kr
     # distinct slots per token and head, as a Top-K decode produces them; token-major storage
@@ -37,8 +37,8 @@ def _case(seed, B, H, T, A, C, Kw, Kr, dev):
     val = torch.rand(B, T, H, KT, device=dev, generator=g) * 0.5 + 0.01
     val[..., Kw:] *= -1  # reads are stored negated
     val[:, 3, :, 1] = 0.0  # a few no-op events
-    x = torch.randn(B, T, H, C, device=dev, generator=g)
-    gamma = torch.randn(B, T, H, device=dev, generator=g) * 0.3
+    x = torch.randn(B, T, H, C, device=dev, generator=g).to(dtype)
+    gamma = (torch.randn(B, T, H, device=dev, generator=g) * 0.3).to(dtype)
     slot = torch.randn(B, H, A, C, device=dev, generator=g)
     mass = torch.rand(B, H, A, device=dev, generator=g) + 0.1
     mask = torch.ones(B, T, dtype=torch.uint8, device=dev)
@@ -50,8 +50,8 @@ def _run(C, lib, static, tensors, dims, mass_aware):
     idx, val, x, gamma, slot, mass, mask = tensors
     B, H, T, A, Cc, Kw, Kr = dims
     slot_out, mass_out = torch.empty_like(slot), torch.empty_like(mass)
-    y = torch.empty(B, T, H, Cc, device=x.device).permute(0, 2, 1, 3)
-    common = [C.ptr(idx), C.ptr(val), C.strides(idx), C.ptr(x), C.strides(x), C.ptr(gamma), C.strides(gamma), 0,
+    y = torch.empty(B, T, H, Cc, device=x.device, dtype=x.dtype).permute(0, 2, 1, 3)
+    common = [C.ptr(idx), C.ptr(val), C.strides(idx), C.ptr(x), C.strides(x), C.ptr(gamma), C.strides(gamma), C.dtype_code(x),
               C.ptr(mask), C.strides(mask), C.ptr(slot), C.ptr(mass), C.ptr(slot_out), C.ptr(mass_out), C.ptr(y),
               C.strides(y)]
     tail = [B, H, T, A, Cc, Kw, Kr, int(mass_aware), 1e-6, x.device.index, C.stream_of(x)]
@@ -71,8 +71,10 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     dev = torch.device("cuda", 0)
     assert lib.rn_gsu_static_scratch_bytes() == 32 << 20
     # two different calls in a row: the second one finds the first one's schedule in the array
-    for seed, dims, mass_aware in ((1, (2, 3, 150, 64, 20, 4, 6), False), (2, (1, 4, 70, 256, 8, 8, 3), True)):
-        tensors = _case(seed, *dims, dev)
+    for seed, dims, mass_aware, dtype in ((1, (2, 3, 150, 64, 20, 4, 6), False, torch.float32),
+                                          (2, (1, 4, 70, 256, 8, 8, 3), True, torch.float32),
+                                          (3, (2, 2, 130, 4096, 128, 16, 16), False, torch.bfloat16)):
+        tensors = _case(seed, *dims, dev, dtype)
         want = _run(C, lib, False, tensors, dims, mass_aware)
         got = _run(C, lib, True, tensors, dims, mass_aware)
         for name, a, b in zip(("y", "slot", "mass"), got, want):
