@@ -1,24 +1,29 @@
 """Benchmark of the RAM-Net sparse slot-memory hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload prefill|decode|addr]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" is one pass of the hot path over one batch of seeded synthetic input of the
-BASELINE.json shape (random logits / values of the stated distributions; no dataset is involved):
+One pass of the hot path runs one batch of seeded synthetic input of the benchmark shape (random
+logits / values of the stated distributions; no dataset is involved):
 
   prefill (headline)  B8 T16384 H16 U2 P64 K16 C128 bf16, zero fp32 state: joined address decode
-                      + time-chunked gated sparse update/read.  tokens = B*T per step.
+                      + gated sparse update/read.  tokens = B*T per pass.
   decode              B256 H16 U2 P64 K16 C128, fp32 state 8.6 GB, 1024 one-token steps.
   addr                B8 T8192 H16 U3 P32 K8 bf16 address decode alone.
 
-At N > 1 (torchrun, one rank per GPU) every rank runs the full single-GPU shape on its own batch
-shard (weak scaling, no collective on the data path); the timed region is bracketed by a barrier
-and a device synchronise and the slowest rank's device time counts.
+A timed region has to last a couple of seconds to be a measurement, so one "step" of the K timed
+steps is ``passes_per_step`` passes (stated in ``config``); five regions of K steps are timed and the
+median region is reported.  At N > 1 (torchrun, one rank per GPU) every rank runs the full
+single-GPU shape on its own batch shard (weak scaling, no collective on the data path); the regions
+are bracketed by a barrier and a device synchronise and the slowest rank's device time counts.
+``strong`` holds the same kernels on the benchmark batch SPLIT over the ranks (prefill B = 8 / N,
+decode batch 256 / N per rank).
 
 Prints ONE JSON line.  ``value`` is whole-job tokens/s with inputs resident in HBM; ``e2e`` is the
 same metric through ``ramnet_ops.random_access_memory_attention`` with pinned HOST inputs, the
 host->device copies and the device->host copy of y inside the timed region; ``roofline`` is for the
 dominant kernel, timed with CUDA events recorded on the launch stream inside the library;
-``cpu_baseline`` is the CPU oracle (a port of the reference's algorithm) on a bounded sample.
+``cpu_baseline`` is the CPU oracle (a port of the reference's algorithm) on a bounded sample of the
+same inputs, whose outputs also serve as the parity check of the timed outputs.
 ``--impl reference`` times that CPU port alone with all host threads.
 """
 from __future__ import annotations
@@ -149,12 +154,49 @@ def kernel_times(n):
 # ---------------------------------------------------------------------------------------------
 # workloads (each returns a dict of measurements for this rank)
 # ---------------------------------------------------------------------------------------------
-def run_prefill(args, device, rank, barrier, max_over_ranks):
+REGIONS = 5            # timed regions per measurement; the median region is reported
+REGION_SECONDS = 2.0   # a region is stretched to at least this long by repeating the pass inside a step
+PARITY_HEADS = (6, 10)  # heads of batch row 0 that the CPU sample recomputes: two with the CAPE shift, two without
+PARITY_TOKENS = 4096
+
+
+def median(v):
+    v = sorted(v)
+    return v[len(v) // 2]
+
+
+def timed_regions(fn, passes, barrier, max_over_ranks):
+    """REGIONS regions of `passes` back-to-back calls of fn, each bracketed by barrier + synchronise and CUDA events
+    on the current stream; returns the list of region times in ms (max over ranks)."""
+    out = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(REGIONS):
+        barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(passes):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        out.append(max_over_ranks(e0.elapsed_time(e1)))
+    return out
+
+
+def run_prefill(args, device, rank, barrier, max_over_ranks, batch=None, full=True):
+    """full=False: only the device-resident timing (used for the strong-scaling shard)."""
     import ramnet_ops  # noqa: F401
-    s = SHAPES["prefill"]
+    s = dict(SHAPES["prefill"])
+    if batch is not None:
+        s["B"] = batch
     B, T, H, U, P, K, C, E = (s[k] for k in ("B", "T", "H", "U", "P", "K", "C", "E"))
     A = P ** U
-    dev = make_prefill_inputs(s, device, seed=rank)
+    host = make_prefill_inputs(s, device, seed=rank, pinned_host=True)
+    dev = {n: t.to(device) for n, t in host.items()}
+    sample = None
+    if full and rank == 0:  # the slice of the inputs that the CPU baseline recomputes
+        h0, h1 = PARITY_HEADS
+        sample = {n: host[n][0:1, :PARITY_TOKENS, h0:h1].clone() for n in ("q", "k", "v", "gamma")}
     w_view = dev["k"].permute(0, 2, 3, 4, 1)
     r_view = dev["q"].permute(0, 2, 3, 4, 1)
     x_view = dev["v"].permute(0, 2, 1, 3)
@@ -163,56 +205,62 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
     slot0 = torch.zeros(B, H, A, C, device=device)
     mass0 = torch.full((B, H, A), 1.0 / A, device=device)
     ops = torch.ops.ramnet_ops
+    keep = {}
 
     def step():
         idx, val = ops.topk_addr_forward(w_view, r_view, E, A, pos, K, K, 0.0, 0.0)
-        return ops.gsu_forward(idx, val, x_view, g_view, slot0, mass0, None, K, K, False, 1e-12)
+        keep["out"] = ops.gsu_forward(idx, val, x_view, g_view, slot0, mass0, None, K, K, False, 1e-12)
 
-    out = None
-    for _ in range(args.warmup):
-        out = step()  # kept like in the timed loop, so that the allocator's pool reaches the same steady state
+    for _ in range(max(args.warmup, 3)):
+        step()
     torch.cuda.synchronize()
     # per-kernel device times (events on the launch stream, recorded inside the library)
     lib().rn_prof_enable(1)
-    t_addr, t_sched, t_apply = [], [], []
-    for _ in range(min(args.steps, 5)):
+    t_addr, t_gsu = [], []
+    for _ in range(5):
         idx, val = ops.topk_addr_forward(w_view, r_view, E, A, pos, K, K, 0.0, 0.0)
-        t_addr += kernel_times(4)
+        t_addr.append(sum(kernel_times(4)))
         ops.gsu_forward(idx, val, x_view, g_view, slot0, mass0, None, K, K, False, 1e-12)
-        ts = kernel_times(4)
-        t_sched.append(ts[0])
-        t_apply.append(ts[1])
+        t_gsu.append(kernel_times(4))
+    del idx, val
     lib().rn_prof_enable(0)
     torch.cuda.synchronize()
-
-    barrier()
+    est_ms = median(t_addr) + median([sum(t) for t in t_gsu])
+    passes_per_step = max(1, int(REGION_SECONDS * 1e3 / max(est_ms * args.steps, 1e-3) + 0.999))
+    for _ in range(3):  # the allocator's pool reaches the steady state of the timed loop
+        step()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
     allocs0 = torch.cuda.memory_stats(device).get("num_device_alloc", 0)
     with ClockSampler(torch.cuda.current_device()) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            out = step()
-        e1.record()
-        torch.cuda.synchronize()
-    barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    # cudaMalloc calls inside the timed loop (0 when the caching allocator served every tensor from its pool)
+        regions = timed_regions(step, args.steps * passes_per_step, barrier, max_over_ranks)
+    # cudaMalloc calls inside the timed loops (0 when the caching allocator served every tensor from its pool)
     device_allocs = torch.cuda.memory_stats(device).get("num_device_alloc", 0) - allocs0
-    del out
+    y_dev = keep["out"][0]
+    y_sample = None
+    if sample is not None:
+        h0, h1 = PARITY_HEADS
+        y_sample = y_dev.permute(0, 2, 1, 3)[0:1, :PARITY_TOKENS, h0:h1].float().cpu()   # (1, T', 4, C)
+    keep.clear()
+    names = ["rn_addr_fast_kernel"] + (["rn_gsu_owner_kernel"] if len(t_gsu[0]) == 1 else
+                                       ["rn_gsu_schedule_kernel", "rn_gsu_apply_fast_kernel"])
+    kms = [median(t_addr)] + [median([t[i] for t in t_gsu]) for i in range(len(t_gsu[0]))]
+    result = dict(tokens_per_pass=B * T, regions_ms=regions, passes=args.steps * passes_per_step,
+                  passes_per_step=passes_per_step, clocks=clocks.summary(), kernels=dict(zip(names, kms)),
+                  launches_per_pass=len(names), device_allocs=device_allocs, batch=B)
+    if not full:
+        return result
 
-    # end to end through the public API with pinned host inputs
+    # ---- end to end through the public API with pinned host inputs -----------------------------------------
     import ramnet_ops as ro
-    host = make_prefill_inputs(s, device, seed=rank, pinned_host=True)
     y_host = torch.empty((B, T, H, C), dtype=torch.bfloat16, pin_memory=True)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = y_host.numel() * y_host.element_size()
-
     # Every step copies its inputs from pinned host memory and its output back; the copies of step i+1 /
     # i-1 run on their own streams next to the compute of step i (double-buffered device tensors).
     copy_in, copy_out = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
     main = torch.cuda.current_stream(device)
-    dev_in = [{n: torch.empty_like(t, device=device) for n, t in host.items()} for _ in range(2)]
+    dev_in = [dev, {n: torch.empty_like(t, device=device) for n, t in host.items()}]
     in_ready = [torch.cuda.Event() for _ in range(2)]
     in_free = [torch.cuda.Event() for _ in range(2)]
     out_done = torch.cuda.Event()
@@ -245,19 +293,20 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
                 out_done.record(copy_out)
         main.wait_event(out_done)  # the timed region ends when the last output is on the host
 
-    e2e_steps = max(2, min(args.steps, 6))
+    e2e_steps = max(4, min(args.steps, 8))
     run_e2e(2)
     torch.cuda.synchronize()
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     run_e2e(e2e_steps)
     e1.record()
     torch.cuda.synchronize()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    del y_host, dev_in
 
-    del host, y_host, dev_in
-    # backward of the same step (address backward + update/read backward), timed per kernel
+    # ---- backward of the same pass (address backward + update/read backward), timed per kernel -------------
     bwd = None
     if not args.no_extra:
         idx, val = ops.topk_addr_forward(w_view, r_view, E, A, pos, K, K, 0.0, 0.0)
@@ -284,38 +333,34 @@ def run_prefill(args, device, rank, barrier, max_over_ranks):
         del d_val, d_x, d_g, d_s, d_m, dw, dr, d_y, d_slot, d_mass, idx, val
         torch.cuda.empty_cache()
 
-
-    def mean(v):
-        return sum(v) / max(len(v), 1)
-
-    per_bh = T * (C * 2 + C * 2) + 2 * A * C * 4  # apply kernel: x once, y once, slot state in and out
-    # DRAM traffic of the apply kernel from the ncu capture of the small case (B2 T4096 H16: 139.4 MB read
-    # + 69.3 MB written, profiles/rn_gsu_apply_fast_kernel_prefill_small.md), per (b,t,h); it grows in
-    # proportion to the units processed (event records and x/y rows per token-head)
-    traffic = (139.404544e6 + 69.276672e6) / (2 * 4096 * 16) * (B * T * H)
+    gsu_name = names[-1]
+    per_bh = T * (C * 2 + C * 2) + 2 * A * C * 4  # update/read kernel: x once, y once, slot state in and out
+    if gsu_name == "rn_gsu_owner_kernel":
+        per_bh += T * 2 * K * 8 + T * 2 + 2 * A * 4  # it also reads idx / val and gamma and moves the mass
     step_bytes = B * H * (T * (2 * U * P * 2 + C * 2 + 2 + C * 2) + 2 * A * C * 4 + 2 * A * 4)
-    return dict(
-        tokens_per_step=B * T, ms_total=ms, steps=args.steps, e2e_ms_total=e2e_ms, e2e_steps=e2e_steps,
-        h2d=h2d, d2h=d2h, launches_per_step=3, clocks=clocks.summary(),
-        kernels={"rn_addr_fast_kernel": mean(t_addr), "rn_gsu_schedule_kernel": mean(t_sched),
-                 "rn_gsu_apply_fast_kernel": mean(t_apply)},
-        dominant=("rn_gsu_apply_fast_kernel", B * H * per_bh, mean(t_apply)), step_bytes=step_bytes, bwd=bwd,
-        traffic=traffic, device_allocs=device_allocs,
+    result.update(
+        e2e_ms_total=e2e_ms, e2e_steps=e2e_steps, h2d=h2d, d2h=d2h, bwd=bwd, step_bytes=step_bytes,
+        dominant=(gsu_name, B * H * per_bh, kms[-1]), sample=sample, y_sample=y_sample,
+        plan=__import__("ramnet_ops._C", fromlist=["x"]).gsu_plan_info(B, H, T, A, C, K, K),
         workload="prefill_fwd B8 T16384 H16 U2 P64(A4096) Kw16 Kr16 C128 bf16, CAPE on 8 heads, zero fp32 state")
+    return result
 
 
-def run_decode(args, device, rank, barrier, max_over_ranks, steps=None):
+def run_decode(args, device, rank, barrier, max_over_ranks, steps=None, batch=None, check=False):
     import ramnet_ops  # noqa: F401
     s = SHAPES["decode"]
     B, H, U, P, K, C, E = (s[k] for k in ("B", "H", "U", "P", "K", "C", "E"))
+    if batch is not None:
+        B = batch
     A = P ** U
     nsteps = steps or s["T"]
     g = torch.Generator(device=device).manual_seed(100 + rank)
     slot = torch.empty(B, H, A, C, device=device)
     for b in range(0, B, 16):
-        slot[b:b + 16] = torch.randn(16, H, A, C, device=device, generator=g) * 0.1
+        nb = min(16, B - b)
+        slot[b:b + nb] = torch.randn(nb, H, A, C, device=device, generator=g) * 0.1
     mass = torch.rand(B, H, A, device=device, generator=g) + 0.1
-    nbuf = 16  # rotate through a few input sets; the 8.6 GB state is the traffic that matters
+    nbuf = 16  # rotate through a few input sets; the state is the traffic that matters
     q = torch.randn(nbuf, B, H, U, P, device=device, generator=g).bfloat16()
     k = torch.randn(nbuf, B, H, U, P, device=device, generator=g).bfloat16()
     v = torch.randn(nbuf, B, H, C, device=device, generator=g).bfloat16()
@@ -334,10 +379,19 @@ def run_decode(args, device, rank, barrier, max_over_ranks, steps=None):
     torch.cuda.synchronize()
     lib().rn_prof_enable(1)
     tk = []
-    for i in range(8):
+    for i in range(16):
         one(i)
         tk += kernel_times(2)
     lib().rn_prof_enable(0)
+    # eager loop: one operator call per step from Python, events around the loop
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(64):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    eager_ms = e0.elapsed_time(e1) / 64
     # the timed loop replays a CUDA graph of nbuf steps (the operator plus the on-device position increment):
     # launched step by step from Python the loop is bound by the host, not by the kernel
     from ramnet_ops import DecodeGraph
@@ -346,21 +400,21 @@ def run_decode(args, device, rank, barrier, max_over_ranks, steps=None):
     replays = max(1, nsteps // nbuf)
     nsteps = replays * nbuf
     graph.replay()
-    barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(replays):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
+    regions = timed_regions(graph.replay, replays, barrier, max_over_ranks)
+    ms = median(regions)
     per_bh = 2 * U * P * 2 + C * 2 + 2 + 2 * K * C * 4 + 2 * K * 4 + K * C * 4 + C * 2
-    kt = sum(tk) / max(len(tk), 1)
-    return dict(tokens_per_s=B * nsteps / (ms / 1e3), ms_per_step=ms / nsteps, kernel_ms=kt,
-                kernel_gbs=B * H * per_bh / (kt / 1e3) / 1e9 if kt > 0 else None, bytes_per_step=B * H * per_bh,
-                steps=nsteps)
+    kt = median(tk)
+    out = dict(tokens_per_s=B * nsteps / (ms / 1e3), ms_per_step=ms / nsteps, kernel_ms=kt, eager_ms_per_step=eager_ms,
+               bytes_per_step=B * H * per_bh, steps=nsteps, regions_ms=regions, batch=B)
+    if check:
+        # one more step on known inputs: batch row 0 before and after, for the CPU oracle
+        row_slot, row_mass = slot[0:1].cpu(), mass[0:1].cpu()
+        pos.fill_(7)
+        y = ops.topk_autoregressive_(k[3], q[3], v[3], gm[3], slot, mass, nomask, E, pos, K, K, 0.0, 0.0, False, 1e-12)
+        out["check"] = dict(w=k[3][0:1].float().cpu(), r=q[3][0:1].float().cpu(), x=v[3][0:1].float().cpu(),
+                            g=gm[3][0:1].float().cpu(), slot=row_slot, mass=row_mass, y=y[0:1].float().cpu(),
+                            slot_after=slot[0:1].cpu(), mass_after=mass[0:1].cpu())
+    return out
 
 
 def run_addr(args, device, rank, barrier, max_over_ranks):
@@ -389,31 +443,58 @@ def run_addr(args, device, rank, barrier, max_over_ranks):
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU baseline: the oracle port on a bounded sample of the prefill workload
+# CPU baseline: the oracle port on a bounded sample of the prefill workload (and the parity check)
 # ---------------------------------------------------------------------------------------------
-def cpu_baseline(reps=1):
+def close_enough(got, want, atol, rtol, max_bad):
+    err = (got.double() - want.double()).abs() / (atol + rtol * want.double().abs())
+    return bool(torch.isfinite(got).all()) and float((err > 1).double().mean()) <= max_bad
+
+
+def cpu_baseline(reps=1, sample=None, y_sample=None, decode_check=None):
+    """Times the oracle on B1 x 4 heads x 4096 tokens of the prefill workload.  With `sample` (that slice of the
+    inputs the GPU ran) the oracle's output is also compared with the GPU's y for the same tokens; with
+    `decode_check` one decode step of one batch row is compared as well."""
     from oracle import ramnet_oracle as orc
     s = SHAPES["prefill"]
-    B, H, T = 1, 4, 4096
-    U, P, K, C, E = s["U"], s["P"], s["K"], s["C"], 2
+    B, H, T = 1, PARITY_HEADS[1] - PARITY_HEADS[0], PARITY_TOKENS
+    U, P, K, C = s["U"], s["P"], s["K"], s["C"]
+    E = max(0, min(PARITY_HEADS[1], s["E"]) - PARITY_HEADS[0])
     A = P ** U
-    g = torch.Generator().manual_seed(0)
-    w = torch.randn(B, T, H, U, P, generator=g).bfloat16().float().permute(0, 2, 3, 4, 1)
-    r = torch.randn(B, T, H, U, P, generator=g).bfloat16().float().permute(0, 2, 3, 4, 1)
-    x = torch.randn(B, T, H, C, generator=g).bfloat16().float().permute(0, 2, 1, 3)
-    gm = torch.sigmoid(torch.randn(B, T, H, generator=g) + 1).bfloat16().float().permute(0, 2, 1)
+    if sample is None:
+        g = torch.Generator().manual_seed(0)
+        sample = dict(k=torch.randn(B, T, H, U, P, generator=g).bfloat16(), q=torch.randn(B, T, H, U, P, generator=g).bfloat16(),
+                      v=torch.randn(B, T, H, C, generator=g).bfloat16(),
+                      gamma=torch.sigmoid(torch.randn(B, T, H, generator=g) + 1).bfloat16())
+    w = sample["k"].float().permute(0, 2, 3, 4, 1)
+    r = sample["q"].float().permute(0, 2, 3, 4, 1)
+    x = sample["v"].float().permute(0, 2, 1, 3)
+    gm = sample["gamma"].float().permute(0, 2, 1)
     slot, mass = torch.zeros(B, H, A, C), torch.full((B, H, A), 1.0 / A)
     pos = torch.arange(T).view(1, T)
-    best = float("inf")
+    best, y = float("inf"), None
     for _ in range(reps + 1):
         t0 = time.perf_counter()
-        orc.ram_attn(w, r, x, gm, slot, mass, None, E, pos, (K, K))
+        y, _, _ = orc.ram_attn(w, r, x, gm, slot, mass, None, E, pos, (K, K))
         best = min(best, time.perf_counter() - t0)
     # tokens carry all 16 heads in the metric; the sample ran H=4 of them
     tokens = B * T * H / s["H"]
-    return dict(value=tokens / best, unit="tokens/s", cores=torch.get_num_threads(), kind="port",
-                sample=f"oracle.ram_attn on B{B} H{H} T{T} U{U} P{P} K{K} C{C} fp32 (bf16-quantised inputs), "
-                       f"scaled to {s['H']}-head tokens; {best:.2f} s")
+    out = dict(value=tokens / best, unit="tokens/s", cores=torch.get_num_threads(), kind="port",
+               sample=f"oracle.ram_attn on batch row 0, heads {PARITY_HEADS[0]}-{PARITY_HEADS[1] - 1}, first {T} tokens of the "
+                      f"prefill inputs (U{U} P{P} K{K} C{C}, bf16-quantised values in fp32), scaled to {s['H']}-head tokens; "
+                      f"{best:.2f} s")
+    parity = None
+    if y_sample is not None:
+        ok = close_enough(y_sample, y.permute(0, 2, 1, 3), 7.5e-2, 7.5e-2, 0.02)
+        parity = {"prefill_y": "ok" if ok else "MISMATCH"}
+        if decode_check is not None:
+            d = decode_check
+            dec = SHAPES["decode"]
+            ry, rs, rm = orc.decode_step(d["w"], d["r"], d["x"], d["g"], d["slot"], d["mass"], None, dec["E"],
+                                         torch.full((1,), 7), (dec["K"], dec["K"]))
+            ok_d = (close_enough(d["y"], ry, 7.5e-2, 7.5e-2, 0.02) and close_enough(d["slot_after"], rs, 5e-4, 5e-4, 0.01)
+                    and close_enough(d["mass_after"], rm, 5e-4, 5e-4, 0.01))
+            parity["decode_row"] = "ok" if ok_d else "MISMATCH"
+    return out, parity
 
 
 def run_ncu_case(name):
@@ -511,7 +592,7 @@ def main():
         for _ in range(max(args.warmup, 0)):
             cpu_baseline(0)
         for _ in range(max(1, min(args.steps, 5))):
-            vals.append(cpu_baseline(0))
+            vals.append(cpu_baseline(0)[0])
         v = sorted(x["value"] for x in vals)[len(vals) // 2]
         base = vals[0]
         base["value"] = v
@@ -548,58 +629,109 @@ def main():
     extra = {}
     if not args.no_extra:
         torch.cuda.empty_cache()
-        d = run_decode(args, device, rank, barrier, max_over_ranks)
+        d = run_decode(args, device, rank, barrier, max_over_ranks, check=(rank == 0 and world == 1))
         torch.cuda.empty_cache()
         a = run_addr(args, device, rank, barrier, max_over_ranks)
         extra = {"decode": d, "addr": a}
+        torch.cuda.empty_cache()
+        if world > 1:
+            # the benchmark batch split over the ranks (strong scaling): prefill B = 8 / N, decode batch 256 / N
+            sp = run_prefill(args, device, rank, barrier, max_over_ranks, batch=max(1, SHAPES["prefill"]["B"] // world), full=False)
+            torch.cuda.empty_cache()
+            sd = run_decode(args, device, rank, barrier, max_over_ranks, batch=max(1, SHAPES["decode"]["B"] // world))
+            torch.cuda.empty_cache()
+            extra["strong"] = (sp, sd)
 
     peak, peak_kind = peaks()
     name, alg_bytes, kms = m["dominant"]
     achieved = alg_bytes / (kms / 1e3) / 1e9
-    ms_per_step = m["ms_total"] / m["steps"]
-    value = world * m["tokens_per_step"] / (ms_per_step / 1e3)
-    e2e_value = world * m["tokens_per_step"] / (m["e2e_ms_total"] / m["e2e_steps"] / 1e3)
+    region_ms = median(m["regions_ms"])
+    ms_per_pass = region_ms / m["passes"]
+    ms_per_step = region_ms / args.steps
+    value = world * m["tokens_per_pass"] / (ms_per_pass / 1e3)
+    e2e_value = world * m["tokens_per_pass"] / (m["e2e_ms_total"] / m["e2e_steps"] / 1e3)
     line = {
         "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": m["workload"], "io_dtype": "bf16", "state_dtype": "f32", "per_gpu_batch": SHAPES["prefill"]["B"],
-                   "l2": "inputs_exceed_l2 (1.3 GB per step)", "sharding": "batch, no data-path collective"},
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"]},
-        "gpu_launches": m["launches_per_step"] * args.steps, "device_allocs_in_timed_loop": m["device_allocs"],
-        "clocks": m["clocks"],
+                   "passes_per_step": m["passes_per_step"], "ms_per_pass": ms_per_pass,
+                   "timing": f"median of {REGIONS} regions of steps x passes_per_step passes each",
+                   "l2": "inputs_exceed_l2 (1.3 GB per pass)", "sharding": "batch, no data-path collective", "plan": m["plan"]},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"],
+                "steps": m["e2e_steps"], "passes_per_step": 1},
+        "gpu_launches": m["launches_per_pass"] * m["passes"] * REGIONS, "device_allocs_in_timed_loop": m["device_allocs"],
+        "regions_ms": m["regions_ms"], "clocks": m["clocks"],
         "roofline": {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": m["traffic"],
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic_of(name, m),
+                     "traffic_scaled_from": TRAFFIC.get(name, {}).get("capture"),
                      "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kms},
-        "roofline_step": {"algorithmic_bytes": m["step_bytes"], "achieved": m["step_bytes"] / (ms_per_step / 1e3) / 1e9,
-                          "frac": m["step_bytes"] / (ms_per_step / 1e3) / 1e9 / peak},
+        "roofline_step": {"algorithmic_bytes": m["step_bytes"], "achieved": m["step_bytes"] / (ms_per_pass / 1e3) / 1e9,
+                          "frac": m["step_bytes"] / (ms_per_pass / 1e3) / 1e9 / peak},
         "kernel_ms": m["kernels"],
     }
     if m.get("bwd"):
         bw = m["bwd"]
         bwd_bytes = SHAPES["prefill"]["B"] * SHAPES["prefill"]["H"] * 35.7e6
-        line["prefill_bwd"] = {"kernel_ms": bw, "fwd_plus_bwd_tokens_per_s": world * m["tokens_per_step"] /
-                               ((ms_per_step + bw["total_ms"]) / 1e3),
-                               "algorithmic_bytes": bwd_bytes, "frac": bwd_bytes / (bw["total_ms"] / 1e3) / 1e9 / peak}
+        fb = world * m["tokens_per_pass"] / ((ms_per_pass + bw["total_ms"]) / 1e3)
+        line["prefill_bwd"] = {"kernel_ms": bw, "fwd_plus_bwd_tokens_per_s": fb, "algorithmic_bytes": bwd_bytes,
+                               "frac": bwd_bytes / (bw["total_ms"] / 1e3) / 1e9 / peak}
+        line["fwd_bwd_tokens_per_s"] = fb   # second headline: the benchmark config is forward plus backward
     if extra:
         d, a = extra["decode"], extra["addr"]
         # achieved bandwidth from the graph-replayed step time (kernel plus position increment, back to back);
         # kernel_ms is the same kernel bracketed by events in eager mode, event overhead included
         dec_gbs = d["bytes_per_step"] / (d["ms_per_step"] / 1e3) / 1e9
         line["decode"] = {"tokens_per_s": world * d["tokens_per_s"], "ms_per_step": d["ms_per_step"], "kernel_ms": d["kernel_ms"],
-                          "achieved_gbs": dec_gbs, "frac": dec_gbs / peak, "timing": "cuda_graph_replay",
+                          "eager_ms_per_step": d["eager_ms_per_step"],
+                          "achieved_gbs": dec_gbs, "frac": dec_gbs / peak, "timing": "cuda_graph_replay, median of 5 regions",
                           "algorithmic_bytes_per_step": d["bytes_per_step"], "steps": d["steps"],
                           "workload": "decode B256 H16 U2 P64 K16 C128, fp32 state 8.6 GB"}
         line["addr"] = {"tokens_per_s": world * a["tokens_per_s"], "kernel_ms": a["kernel_ms"], "achieved_gbs": a["kernel_gbs"],
                         "frac": a["kernel_gbs"] / peak, "algorithmic_bytes": a["bytes"],
                         "workload": "addr B8 T8192 H16 U3 P32 K8 bf16"}
+        if "strong" in extra:
+            sp, sd = extra["strong"]
+            sp_ms = median(sp["regions_ms"]) / sp["passes"]
+            line["strong"] = {
+                "prefill_tokens_per_s": world * sp["tokens_per_pass"] / (sp_ms / 1e3), "prefill_ms_per_pass": sp_ms,
+                "prefill_batch_per_rank": sp["batch"], "decode_tokens_per_s": world * sd["tokens_per_s"],
+                "decode_ms_per_step": sd["ms_per_step"], "decode_batch_per_rank": sd["batch"],
+                "note": "total work fixed: the benchmark batch split over the ranks, no data-path collective"}
+        else:
+            line["strong"] = {"prefill_tokens_per_s": value, "prefill_batch_per_rank": SHAPES["prefill"]["B"],
+                              "decode_tokens_per_s": d["tokens_per_s"], "decode_batch_per_rank": d["batch"],
+                              "note": "one rank: the split batch is the whole batch"}
     if rank == 0:
         if world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
-            line["cpu_baseline"] = cpu_baseline(1)
+            base, parity = cpu_baseline(1, m["sample"], m["y_sample"], extra.get("decode", {}).get("check") if extra else None)
+            line["cpu_baseline"] = base
+            line["parity_check"] = parity
+            if parity and any(v != "ok" for v in parity.values()):
+                line["parity_check"]["verdict"] = "FAILED: the timed outputs do not match the oracle"
+        else:
+            line["parity_check"] = "not run at N > 1 (the CPU sample runs at N = 1)"
         emit(line)
     if dist is not None:
         dist.destroy_process_group()
+
+
+# DRAM traffic of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of a SMALL
+# case, per (b,t,h), to be scaled to the benchmark shape by the token-heads processed (the traffic is x / y rows,
+# decoded addresses and the state round trip, all proportional to them at fixed T).  None: no capture yet.
+TRAFFIC = {
+    "rn_gsu_apply_fast_kernel": {"bytes_per_bth": (139.404544e6 + 69.276672e6) / (2 * 4096 * 16),
+                                 "capture": "ncu, --ncu-case prefill_small (B2 T4096 H16), scaled by token-heads"},
+}
+
+
+def traffic_of(name, m):
+    t = TRAFFIC.get(name)
+    if t is None:
+        return None
+    s = SHAPES["prefill"]
+    return t["bytes_per_bth"] * s["B"] * s["T"] * s["H"]
 
 
 if __name__ == "__main__":

@@ -154,6 +154,20 @@ int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const 
  */
 int64_t rn_gsu_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
                                int device);
+/* The same query for a caller that knows the dtype and whether the rows of x start on 16-byte boundaries
+ * (base pointer and the B, H, T strides in bytes all multiples of 16).  Model shapes (C = 128, A a multiple of
+ * 16 up to 4096, Kr <= 16, Kw + Kr <= 32, 16-bit values) can run on the slot-owner kernel (when enabled, see
+ * rn_gsu_owner_enable), which keeps the state of a (batch, head) in the shared memory of one 16-CTA cluster and
+ * needs NO workspace: the answer is then 0 and rn_gsu_fwd accepts workspace == NULL.
+ * rn_gsu_workspace_bytes() is always sufficient. */
+/* The slot-owner kernel is an alternative forward path, off by default (on B200 the channel-slice kernels are
+ * faster); rn_gsu_owner_enable(1) switches it on for the process, returns the previous setting (-1 = never set,
+ * then the environment variable RN_PREFILL_OWNER=1 decides).  rn_gsu_owner_profile() hands it a device buffer
+ * of 8 int64 cycle counters that CTA 0 fills (NULL = off); a benchmark aid.  No counterpart in the reference. */
+int rn_gsu_owner_enable(int on);
+int rn_gsu_owner_profile(long long *device_counters);
+int64_t rn_gsu_fwd_workspace_bytes(int dtype, int rows_aligned, int64_t B, int64_t H, int64_t T, int64_t A, int64_t C,
+                                   int64_t Kw, int64_t Kr, int device);
 /* Launch plan of a prefill call of this shape (no counterpart in the reference; its launch geometry is fixed,
  * packages/ramnet-ops/csrc/ram_attn_segment_parallel.cu:785-830).  Fills out[0..7]: fast apply kernel (1/0),
  * channels per CTA, events per thread (forward), channel slices, chunk length, state slice in shared memory

@@ -766,6 +766,22 @@ extern "C" int rn_gsu_plan_info(int64_t B, int64_t H, int64_t T, int64_t A, int6
     return 0;
 }
 
+extern "C" int64_t rn_gsu_fwd_workspace_bytes(int dtype, int rows_aligned, int64_t B, int64_t H, int64_t T, int64_t A,
+                                              int64_t C, int64_t Kw, int64_t Kr, int device) {
+    rn_clear_error();
+    RnGsuPlan pl;
+    if (rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return -1;
+    if (rows_aligned) {
+        alignas(16) static const char probe[16] = {0};
+        const int64_t ok_strides[4] = {8, 8, 8, 1};
+        RnDeviceGuard guard(device);
+        if (guard.ok && rn_gsu_owner_eligible(dtype, A, C, Kw, Kr, probe, ok_strides, probe, ok_strides) &&
+            rn_gsu_owner_clusters(dtype, device) > 0)
+            return 0;
+    }
+    return int64_t(pl.total);
+}
+
 template <typename T, bool SMEM>
 static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int bh = p.B * p.H;
@@ -837,21 +853,48 @@ extern "C" int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *i
                           int64_t Kr, int mass_aware, double eps, int device, void *stream_) {
     rn_clear_error();
     RN_REQUIRE(idx && val && idx_strides && x && x_strides && gamma && gamma_strides && slot_in && mass_in && slot_out &&
-                   mass_out && y && y_strides && workspace,
+                   mass_out && y && y_strides,
                "null pointer argument");
     RN_REQUIRE(dtype == RN_F32 || dtype == RN_F16 || dtype == RN_BF16, "unsupported dtype code %d", dtype);
     RN_REQUIRE(x_strides[3] == 1 && y_strides[3] == 1, "Tensor x / y last dim must be contiguous");
     RN_REQUIRE(mask == nullptr || mask_strides != nullptr, "mask needs strides");
     RnGsuPlan pl;
     if (int rc = rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return rc;
-    RN_REQUIRE(workspace_bytes >= int64_t(pl.total), "workspace too small: %lld < %lld bytes", (long long)workspace_bytes,
-               (long long)pl.total);
-    RN_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
     RN_REQUIRE((reinterpret_cast<uintptr_t>(slot_in) & 15) == 0 && (reinterpret_cast<uintptr_t>(slot_out) & 15) == 0,
                "slot state must be 16-byte aligned");
     RnDeviceGuard guard(device);
     RN_REQUIRE(guard.ok, "cannot make device %d current", device);
     cudaStream_t stream = cudaStream_t(stream_);
+
+    // model shapes: the slot-owner kernel (one cluster per (b,h)), which needs no schedule and no workspace
+    if (rn_gsu_owner_eligible(dtype, A, C, Kw, Kr, x, x_strides, y, y_strides)) {
+        RnGsuParams q{};
+        q.idx = idx; q.val = val;
+        q.ib = idx_strides[0]; q.ih = idx_strides[1]; q.ik = idx_strides[2]; q.it = idx_strides[3];
+        q.x = x; q.xb = x_strides[0]; q.xh = x_strides[1]; q.xt = x_strides[2];
+        q.gamma = gamma; q.gb = gamma_strides[0]; q.gh = gamma_strides[1]; q.gt = gamma_strides[2];
+        q.mask = mask;
+        if (mask) { q.mb = mask_strides[0]; q.mt = mask_strides[1]; }
+        q.y = y; q.yb = y_strides[0]; q.yh = y_strides[1]; q.yt = y_strides[2];
+        q.slot_in = slot_in; q.slot_out = slot_out; q.mass_in = mass_in; q.mass_out = mass_out;
+        q.B = int(B); q.H = int(H); q.T = int(T); q.A = int(A); q.C = int(C); q.Kw = int(Kw); q.Kr = int(Kr);
+        q.mass_aware = mass_aware; q.eps = float(eps);
+        q.status = rn_status_word(device);
+        RN_REQUIRE(q.status != nullptr, "cannot locate the status word of device %d", device);
+        rn_prof_reset();
+        rn_prof_mark(stream);
+        const int rc = rn_gsu_owner_launch(q, dtype, device, stream);
+        if (rc == 0) {
+            RN_CUDA(cudaGetLastError());
+            rn_prof_mark(stream);
+            return 0;
+        }
+        if (rc > 0) return rc;
+        // rc < 0: this device cannot keep a 16-CTA cluster of that size resident; use the channel-slice kernels
+    }
+    RN_REQUIRE(workspace != nullptr && workspace_bytes >= int64_t(pl.total), "workspace too small: %lld < %lld bytes",
+               (long long)workspace_bytes, (long long)pl.total);
+    RN_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
 
     RnGsuParams p{};
     p.idx = idx; p.val = val;

@@ -150,6 +150,14 @@ int rn_gsu_plan(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t K
 int rn_gsu_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, int dtype, cudaStream_t stream);
 inline size_t rn_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// ---- slot-owner forward kernel (rn_prefill_owner.cu): one 16-CTA cluster per (b,h), no schedule workspace ----
+bool rn_gsu_owner_eligible(int dtype, int64_t A, int64_t C, int64_t Kw, int64_t Kr, const void *x, const int64_t *x_strides,
+                           const void *y, const int64_t *y_strides);
+// 0 = launched, -1 = this device cannot keep such a cluster resident (nothing launched), > 0 error (message set)
+int rn_gsu_owner_launch(const RnGsuParams &p, int dtype, int device, cudaStream_t stream);
+// resident 16-CTA clusters of the kernel on this device (0 = cannot run)
+int rn_gsu_owner_clusters(int dtype, int device);
+
 // ---- mbarrier / bulk-copy (TMA 1-D) primitives -----------------------------------------------
 __device__ __forceinline__ uint32_t rn_smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
 

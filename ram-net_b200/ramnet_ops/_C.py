@@ -41,6 +41,12 @@ lib.rn_decode_step.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _
 
 lib.rn_gsu_workspace_bytes.restype = ctypes.c_int64
 lib.rn_gsu_workspace_bytes.argtypes = [_i64] * 7 + [_i32]
+lib.rn_gsu_fwd_workspace_bytes.restype = ctypes.c_int64
+lib.rn_gsu_fwd_workspace_bytes.argtypes = [_i32, _i32] + [_i64] * 7 + [_i32]
+lib.rn_gsu_owner_enable.restype = ctypes.c_int
+lib.rn_gsu_owner_enable.argtypes = [_i32]
+lib.rn_gsu_owner_profile.restype = ctypes.c_int
+lib.rn_gsu_owner_profile.argtypes = [_ptr]
 lib.rn_gsu_plan_info.restype = ctypes.c_int
 lib.rn_gsu_plan_info.argtypes = [_i64] * 7 + [_i32, _i32, ctypes.POINTER(ctypes.c_int32), _i32]
 lib.rn_gsu_fwd.restype = ctypes.c_int
@@ -101,7 +107,11 @@ def gsu_plan_info(B, H, T, A, C, Kw, Kr, reverse=False, device=0) -> dict:
     out = (ctypes.c_int32 * 8)()
     check(lib.rn_gsu_plan_info(B, H, T, A, C, Kw, Kr, int(reverse), device, out, 8))
     names = ("fast", "cs", "ev", "nslices", "L", "state_in_smem", "ev_bwd", "smem_tables")
-    return dict(zip(names, (int(v) for v in out)))
+    info = dict(zip(names, (int(v) for v in out)))
+    # forward of 16-bit values with 16-byte aligned rows: 1 when the slot-owner cluster kernel takes the call
+    # (it needs no workspace), 0 when the channel-slice kernels do
+    info["owner_16bit"] = int(lib.rn_gsu_fwd_workspace_bytes(DTYPE_CODE[torch.bfloat16], 1, B, H, T, A, C, Kw, Kr, device) == 0)
+    return info
 
 
 def strides(t: torch.Tensor):

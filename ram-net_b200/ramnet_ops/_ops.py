@@ -174,6 +174,8 @@ def _topk_addr_single_backward(idx, val, addr, D_val, embed_num, position_ids, t
                                shape, dtype):
     if len(shape) != 6:
         raise RuntimeError("Expected address dimensions (B, H, U, P, A, T).")
+    if addr is None or idx is None or val is None or D_val is None:
+        raise RuntimeError("topk_addr_single_backward needs idx, val, addr and D_val")
     # D_val is the gradient of the stored (signed) value; the kernel wants it w.r.t. the positive weight
     d_pos = -D_val if addr_val_neg else D_val
     d_w, _ = addr_backward_impl(idx, val, addr, None, d_pos, embed_num, position_ids, top_k, 0, top_k_re_norm, 0.0,
@@ -286,7 +288,8 @@ def gsu_forward_impl(addr_idx, addr_val, x, gamma, slot_in, mass_in, slot_out, m
     mask_u8 = None
     if mask is not None:
         mask_u8 = mask.to(torch.bool).view(torch.uint8)
-    nbytes = lib.rn_gsu_workspace_bytes(B, H, T, A, C, w_top_k, r_top_k, x.device.index)
+    rows_aligned = x.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in x.stride()[:3])
+    nbytes = lib.rn_gsu_fwd_workspace_bytes(dtype_code(x), int(rows_aligned), B, H, T, A, C, w_top_k, r_top_k, x.device.index)
     if nbytes < 0:
         check(1)
     ws = _workspace(x, nbytes)
@@ -340,7 +343,7 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
     d_gamma = torch.empty((B, H, T), dtype=torch.float32, device=x.device)
     d_slot, d_mass = torch.empty_like(slot_in), torch.empty_like(mass_in)
     if x.numel() == 0:
-        return d_val, d_x[..., :C], d_gamma, d_slot_post[..., :C].clone(), d_mass_post.clone()
+        return d_val, d_x[..., :C].contiguous(), d_gamma, d_slot_post[..., :C].clone(), d_mass_post.clone()
     mask_u8 = None if mask is None else mask.to(torch.bool).view(torch.uint8)
     nbytes = lib.rn_gsu_bwd_workspace_bytes(B, H, T, A, C4, w_top_k, r_top_k, x.device.index)
     if nbytes < 0:
@@ -352,7 +355,9 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
                          ptr(d_x), strides(d_x), ptr(d_gamma), ptr(d_slot), ptr(d_mass), ptr(ws), int(nbytes), B, H, T, A,
                          C4, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
     check_device(d_val)
-    return d_val, d_x[..., :C], d_gamma, d_slot[..., :C], d_mass
+    if C4 != C:  # results of the padded run: hand back dense tensors, as the fake kernel promises
+        return d_val, d_x[..., :C].contiguous(), d_gamma, d_slot[..., :C].contiguous(), d_mass
+    return d_val, d_x, d_gamma, d_slot, d_mass
 
 
 # ----------------------------------------------------------------------------------------------
@@ -389,30 +394,53 @@ def _event_values(addr_val, event_i):
     return addr_val.transpose(-2, -1).reshape(-1).index_select(0, event_i.to(torch.int64))
 
 
+def is_direct(seg_off: torch.Tensor) -> bool:
+    """The update / read operators under the reference's names accept two calling conventions.  SEGMENT form
+    (the reference's): seg_idx / seg_off / seg_len / event_i are the tables of ``gather_segment``.  DIRECT form
+    (this package's own path): ``seg_off`` and ``seg_len`` are empty, ``seg_idx`` is the decoded index tensor
+    (B,H,Kw+Kr,T) itself and ``event_i`` is the token mask (B,T) as uint8, or empty for no mask; y then comes
+    back in the dtype of x, stored token-major, and the replay-cache output is empty."""
+    return seg_off.numel() == 0
+
+
+def _direct_mask(event_i: torch.Tensor):
+    return None if event_i.numel() == 0 else event_i
+
+
 @torch.library.impl(_lib, "topk_segment_forward", "CUDA")
 def _topk_segment_forward(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k,
                           mass_aware, eps):
+    if is_direct(seg_off):
+        y, slot, mass = _gsu_forward(seg_idx, addr_val, x, gamma, init_slot, init_mass, _direct_mask(event_i), w_top_k,
+                                     r_top_k, mass_aware, eps)
+        return y, slot, mass, addr_val.new_empty(0)
     B, H, T, C = x.shape
     A = init_slot.shape[2]
     event_v = _event_values(addr_val, event_i)
     idx, val = _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, w_top_k + r_top_k, A)
     y, slot, mass = _gsu_forward(idx, val, x, gamma, init_slot, init_mass, None, w_top_k, r_top_k, mass_aware, eps)
-    return y.to(torch.float32), slot, mass, event_v
+    return y.to(torch.float32).contiguous(), slot, mass, event_v
 
 
 @torch.library.impl(_lib, "topk_segment_forward_", "CUDA")
 def _topk_segment_forward_(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, slot, mass, w_top_k, r_top_k,
                            mass_aware, eps):
+    if is_direct(seg_off):
+        return gsu_forward_impl(seg_idx, addr_val, x, gamma, slot, mass, slot, mass, _direct_mask(event_i), w_top_k, r_top_k,
+                                mass_aware, eps)
     B, H, T, C = x.shape
     event_v = _event_values(addr_val, event_i)
     idx, val = _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, w_top_k + r_top_k, slot.shape[2])
     y = gsu_forward_impl(idx, val, x, gamma, slot, mass, slot, mass, None, w_top_k, r_top_k, mass_aware, eps)
-    return y.to(torch.float32)
+    return y.to(torch.float32).contiguous()
 
 
 @torch.library.impl(_lib, "topk_segment_backward", "CUDA")
 def _topk_segment_backward(seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, init_slot, init_mass, D_y, D_post_slot,
                            D_post_mass, w_top_k, r_top_k, mass_aware, eps):
+    if is_direct(seg_off):  # event_v carries the decoded weights (B,H,Kw+Kr,T)
+        return _gsu_backward(seg_idx, event_v, x, gamma, init_slot, init_mass, _direct_mask(event_i), D_y.to(x.dtype),
+                             D_post_slot, D_post_mass, w_top_k, r_top_k, mass_aware, eps)
     B, H, T, C = x.shape
     idx, val = _events_to_token_major(seg_idx, seg_off, seg_len, event_i, event_v, B, H, T, w_top_k + r_top_k,
                                       init_slot.shape[2])

@@ -158,30 +158,47 @@ torch.library.register_autograd("ramnet_ops::gsu_forward", _gsu_backward, setup_
 
 
 # ---------------------------------------------------------------------------- event / segment schemas
+# Two calling conventions (see _ops.is_direct): the reference's segment tables, or the direct form in which
+# seg_off is empty and seg_idx / event_i are the decoded indices and the token mask.
+def _direct(seg_off):
+    return seg_off.numel() == 0
+
+
 @torch.library.register_fake("ramnet_ops::topk_segment_forward")
 def _(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k, mass_aware, eps):
-    return (x.new_empty(x.shape, dtype=torch.float32), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
-            init_mass.new_empty(init_mass.shape, dtype=torch.float32), addr_val.new_empty(event_i.shape))
+    slot = init_slot.new_empty(init_slot.shape, dtype=torch.float32)
+    mass = init_mass.new_empty(init_mass.shape, dtype=torch.float32)
+    if _direct(seg_off):
+        return _y_like(x), slot, mass, addr_val.new_empty(0)
+    return x.new_empty(x.shape, dtype=torch.float32), slot, mass, addr_val.new_empty(event_i.shape)
 
 
 @torch.library.register_fake("ramnet_ops::topk_segment_forward_")
 def _(addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, slot, mass, w_top_k, r_top_k, mass_aware, eps):
-    return x.new_empty(x.shape, dtype=torch.float32)
+    return _y_like(x) if _direct(seg_off) else x.new_empty(x.shape, dtype=torch.float32)
 
 
 @torch.library.register_fake("ramnet_ops::topk_segment_backward")
 def _(seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, init_slot, init_mass, D_y, D_post_slot, D_post_mass,
       w_top_k, r_top_k, mass_aware, eps):
     B, H, T, _ = x.shape
-    return (x.new_empty((B, H, w_top_k + r_top_k, T), dtype=torch.float32), x.new_empty(x.shape, dtype=torch.float32),
-            gamma.new_empty(gamma.shape, dtype=torch.float32), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
-            init_mass.new_empty(init_mass.shape, dtype=torch.float32))
+    K = w_top_k + r_top_k
+    d_slot = init_slot.new_empty(init_slot.shape, dtype=torch.float32)
+    d_mass = init_mass.new_empty(init_mass.shape, dtype=torch.float32)
+    if _direct(seg_off):
+        return (_token_major(x, B, H, K, T, torch.float32), x.new_empty(x.shape), x.new_empty((B, H, T), dtype=torch.float32),
+                d_slot, d_mass)
+    return (x.new_empty((B, H, K, T), dtype=torch.float32), x.new_empty(x.shape, dtype=torch.float32),
+            gamma.new_empty(gamma.shape, dtype=torch.float32), d_slot, d_mass)
 
 
 def _segment_setup(ctx, inputs, output):
-    _, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k, mass_aware, eps = inputs
+    addr_val, seg_idx, seg_off, seg_len, event_i, x, gamma, init_slot, init_mass, w_top_k, r_top_k, mass_aware, eps = inputs
     ctx.opts = (w_top_k, r_top_k, mass_aware, eps)
-    ctx.save_for_backward(seg_idx, seg_off, seg_len, event_i, output[3], x, gamma, init_slot, init_mass)
+    # the backward operator wants the weight of every event: the replay cache in the segment form, the decoded
+    # weights themselves in the direct form
+    values = addr_val if _direct(seg_off) else output[3]
+    ctx.save_for_backward(seg_idx, seg_off, seg_len, event_i, values, x, gamma, init_slot, init_mass)
     ctx.mark_non_differentiable(output[3])
     ctx.set_materialize_grads(False)
 
@@ -189,15 +206,20 @@ def _segment_setup(ctx, inputs, output):
 def _segment_backward(ctx, D_y, D_slot, D_mass, D_event_v):
     seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, slot, mass = ctx.saved_tensors
     w_top_k, r_top_k, mass_aware, eps = ctx.opts
+    if D_y is None and D_slot is None and D_mass is None:
+        return (None,) * 13
     d_addr, d_x, d_gamma, d_slot, d_mass = torch.ops.ramnet_ops.topk_segment_backward(
         seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, slot, mass,
         torch.zeros_like(x) if D_y is None else D_y,
-        torch.zeros_like(slot) if D_slot is None else D_slot, torch.zeros_like(mass) if D_mass is None else D_mass,
+        torch.zeros_like(slot, dtype=torch.float32) if D_slot is None else D_slot,
+        torch.zeros_like(mass, dtype=torch.float32) if D_mass is None else D_mass,
         w_top_k, r_top_k, mass_aware, eps)
     need = ctx.needs_input_grad
+    # d_addr is w.r.t. the positive weight of each event; the joined decode stored reads negated and its backward
+    # expects exactly this convention
     return (d_addr if need[0] else None,) + (None,) * 4 + (
         d_x.to(x.dtype) if need[5] else None, d_gamma.to(gamma.dtype) if need[6] else None,
-        d_slot if need[7] else None, d_mass if need[8] else None) + (None,) * 4
+        d_slot.to(slot.dtype) if need[7] else None, d_mass.to(mass.dtype) if need[8] else None) + (None,) * 4
 
 
 torch.library.register_autograd("ramnet_ops::topk_segment_forward", _segment_backward, setup_context=_segment_setup)

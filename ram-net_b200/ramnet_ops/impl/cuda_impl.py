@@ -79,10 +79,13 @@ def _cuda_ram_attn(w_addr, r_addr, xs, gamma, init_slot, init_mass, mask, embed_
     assert all(k <= A for k in top_k), f"Expected top_k <= A={A}, got {top_k}."
     assert isinstance(embed_num, int) and 0 <= embed_num <= H, f"Expected embed_num in [0, {H}], got {embed_num!r}."
     assert A < ADDRESS_LIMIT, f"Address space overflow: A={A}, limit={ADDRESS_LIMIT}."
-    # int32 quantities: per-call slot numbers and event counts (state element offsets are 64-bit)
-    check_int_capacity(B, H, U, P, A, C, T, embed_num, w_k, r_k, B * H * A, B * H * T * (w_k + r_k))
-
     requires_grad = any(t.requires_grad for t in (w_addr, r_addr, xs, gamma, init_slot, init_mass))
+    # int32 quantities: per-call slot numbers and event counts (state element offsets are 64-bit).  T counts
+    # rounded up to a multiple of 32 like the reference's padded length (cuda_impl.py:190-195), so that the
+    # accepted range of T is the same although nothing is padded here.
+    T32 = T if T == 1 and not requires_grad else (T + 31) // 32 * 32
+    check_int_capacity(B, H, U, P, A, C, T32, embed_num, w_k, r_k, B * H * A, B * H * T32 * (w_k + r_k))
+
     position_ids = position_ids.to(device=xs.device, dtype=torch.int32)
     if mask is not None:
         mask = mask.to(device=xs.device, dtype=torch.bool)
@@ -115,11 +118,17 @@ def _cuda_ram_attn(w_addr, r_addr, xs, gamma, init_slot, init_mass, mask, embed_
         return y.unsqueeze(-2), slot, mass
 
     idx, val = torch.ops.ramnet_ops.topk_addr_forward(w_addr, r_addr, embed_num, A, position_ids, w_k, r_k, w_rho, r_rho)
+    # The update / read runs under the reference's operator names (topk_segment_forward[_]) so that traced graphs
+    # show the same operators, in their DIRECT form: the decoded indices themselves stand where the segment table
+    # would be and the token mask where the event list would be; no sort, no event tables (see _ops.py).
+    none = idx.new_empty(0)
+    events = none if mask is None else mask.to(torch.uint8)
     if inplace:
-        y = torch.ops.ramnet_ops.gsu_forward_(idx, val, xs, gamma, init_slot, init_mass, mask, w_k, r_k, mass_aware, eps)
+        y = torch.ops.ramnet_ops.topk_segment_forward_(val, idx, none, none, events, xs, gamma, init_slot, init_mass,
+                                                       w_k, r_k, mass_aware, eps)
         return y, init_slot, init_mass
-    y, slot, mass = torch.ops.ramnet_ops.gsu_forward(idx, val, xs, gamma, init_slot.to(acc), init_mass.to(acc), mask,
-                                                     w_k, r_k, mass_aware, eps)
+    y, slot, mass, _ = torch.ops.ramnet_ops.topk_segment_forward(val, idx, none, none, events, xs, gamma, init_slot.to(acc),
+                                                                 init_mass.to(acc), w_k, r_k, mass_aware, eps)
     return y, slot, mass
 
 
@@ -136,7 +145,8 @@ def _cuda_topk_addr(addr, embed_num, position_ids, top_k, top_k_re_norm, addr_va
     assert isinstance(addr_val_neg, bool), f"Expected boolean addr_val_neg, got {addr_val_neg!r}."
     assert isinstance(encode_batch_idx, bool), f"Expected boolean encode_batch_idx, got {encode_batch_idx!r}."
     assert tuple(position_ids.shape) == (B, T), f"Expected position_ids.shape={(B, T)}, got {tuple(position_ids.shape)}."
-    check_int_capacity(B, H, U, P, A, T, embed_num, top_k, B * H * A, B * H * top_k * T)
+    T32 = (T + 31) // 32 * 32  # same accepted range of T as the reference, which pads T to a multiple of 32
+    check_int_capacity(B, H, U, P, A, T32, embed_num, top_k, B * H * U * P * T32, B * H * A, B * H * top_k * T32)
     position_ids = position_ids.to(device=addr.device, dtype=torch.int32)
     return torch.ops.ramnet_ops.topk_addr_single_forward(addr, embed_num, A, position_ids, top_k, float(top_k_re_norm),
                                                          addr_val_neg, encode_batch_idx)

@@ -96,6 +96,64 @@ def test_prefill_matches_oracle(case):
     assert got[0].dtype == dtype
 
 
+# shapes the slot-owner cluster kernel takes (C = 128, A a multiple of 16 up to 4096, 16-bit values)
+OWNER_CASES = [
+    # B, H, U, P, T, K, dtype, masked, mass_aware
+    (2, 3, 2, 64, 200, (16, 16), torch.bfloat16, False, False),
+    (1, 2, 2, 64, 130, (16, 16), torch.bfloat16, True, True),
+    (2, 2, 2, 32, 100, (8, 8), torch.float16, True, False),      # A = 1024: 64 rows per CTA
+    (1, 4, 2, 16, 300, (4, 6), torch.bfloat16, False, True),     # A = 256: 16 rows per CTA, one per worker warp
+    (1, 2, 4, 4, 70, (16, 16), torch.bfloat16, True, False),
+    (1, 1, 2, 64, 64, (3, 16), torch.bfloat16, False, False),    # exactly one chunk
+    (1, 2, 3, 16, 90, (12, 5), torch.float16, False, True),
+    (1, 2, 2, 4, 150, (4, 8), torch.bfloat16, False, True),      # A = 16: one row per CTA, > 32 events per warp and chunk
+    (1, 2, 2, 4, 150, (2, 3), torch.bfloat16, True, False),      # A = 16, long same-row chains inside the fast path
+    (3, 5, 2, 64, 1, (16, 16), torch.bfloat16, False, False),    # a single token with gradients-style entry (T = 1)
+]
+
+
+@pytest.fixture
+def owner_kernel():
+    """Switch the slot-owner forward kernel on for one test (it is off by default)."""
+    C_ = ops()
+    C_.lib.rn_gsu_owner_enable(1)
+    yield C_
+    C_.lib.rn_gsu_owner_enable(0)
+
+
+@pytest.mark.parametrize("case", OWNER_CASES)
+def test_owner_kernel_matches_oracle_and_the_channel_slice_kernels(case, owner_kernel):
+    C_ = owner_kernel
+    B, H, U, P, T, K, dtype, masked, ma = case
+    C, A = 128, P ** U
+    assert C_.gsu_plan_info(B, H, T, A, C, K[0], K[1])["owner_16bit"], "the device must keep a 16-CTA cluster resident"
+    w, r, x, g, slot, mass, mask, pos = make_case(B, H, U, P, T, C, dtype, 23, masked=masked)
+    slot = slot * 0.1
+    renorm, eps, E = (0.25, 0.75), 1e-6, H // 2
+    got = run_gpu(w, r, x, g, slot, mass, mask, E, pos, K, renorm, ma, eps)
+    ref = orc.ram_attn(w.float(), r.float(), x.float(), g.float(), slot, mass, mask, E, pos, K, renorm, ma, eps)
+    check("owner", got, ref, mask, dtype)
+    assert got[0].dtype == dtype
+    # the same 16-bit values handed over as fp32 run on the channel-slice kernels; the address decode sees the
+    # same numbers, every slot sees the same operations in the same order: the state is equal bit for bit
+    dev = "cuda"
+    idx, val = torch.ops.ramnet_ops.topk_addr_forward(w.to(dev), r.to(dev), E, A, pos.to(dev).int(), K[0], K[1], *renorm)
+    m_dev = None if mask is None else mask.to(dev)
+    new = torch.ops.ramnet_ops.gsu_forward(idx, val, x.to(dev), g.to(dev), slot.to(dev), mass.to(dev), m_dev, K[0], K[1], ma, eps)
+    old = torch.ops.ramnet_ops.gsu_forward(idx, val, x.float().to(dev), g.float().to(dev), slot.to(dev), mass.to(dev), m_dev,
+                                           K[0], K[1], ma, eps)
+    new, old = [v.cpu() for v in new], [v.cpu() for v in old]
+    assert torch.equal(new[0], got[0]) and torch.equal(new[1], got[1])
+    assert torch.equal(new[1], old[1]) and torch.equal(new[2], old[2])
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP16_TOL
+    yv, ov = (got[0], old[0]) if mask is None else (got[0].permute(0, 2, 1, 3)[mask], old[0].permute(0, 2, 1, 3)[mask])
+    assert_close_stats("y vs channel-slice", yv.float(), ov, **tol)
+    # in place on the same inputs: identical results
+    inpl = run_gpu(w, r, x, g, slot, mass, mask, E, pos, K, renorm, ma, eps, inplace=True)
+    for a, b in zip(got, inpl):
+        assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("name", ["ram_config1.npz", "ram_grads_masked.npz", "ram_grads_massaware.npz",
                                   "ram_grads_plain.npz", "ram_bf16_u2p16.npz"])
 def test_prefill_matches_reference_golden(name):
