@@ -443,6 +443,185 @@ def run_addr(args, device, rank, barrier, max_over_ranks):
 
 
 # ---------------------------------------------------------------------------------------------
+# twin shapes: the reference's own CUDA kernels only take radix P <= 8, so they cannot run the benchmark shapes;
+# shapes with the same slot count and P <= 8 are timed on both implementations through the same public API
+# (random_access_memory_attention / topk_addr).  The reference package (its Python files plus its extension built
+# for sm_100 from the unmodified sources) is looked for under baseline/_ref/ops_pkg and runs in a subprocess,
+# because both packages are called `ramnet_ops`.
+# ---------------------------------------------------------------------------------------------
+TWIN_SHAPES = {
+    # name: (kind, B, T, H, U, P, K, C, dtype)
+    "addr_U5P8_K8 (config-2 twin, 32768 slots)": ("addr", 8, 8192, 16, 5, 8, 8, 0, "bfloat16"),
+    "prefill_U4P8_K16_C128 (config-3 twin, 4096 slots)": ("prefill", 4, 8192, 16, 4, 8, 16, 128, "bfloat16"),
+    "decode_U4P8_K16_C128 (config-4 twin, 4096 slots)": ("decode", 64, 1, 16, 4, 8, 16, 128, "bfloat16"),
+    "prefill_U4P4_K4_C64 (config-1 twin, 256 slots)": ("prefill", 1, 512, 4, 4, 4, 4, 64, "float32"),
+}
+TWIN_REF_DIR = ROOT / "baseline" / "_ref" / "ops_pkg"
+
+
+def twin_times(tag):
+    """Time every twin shape with whichever `ramnet_ops` is first on the import path; returns {name: ms}."""
+    import ramnet_ops as ro
+    device = torch.device("cuda", 0)
+    out = {"package": str(Path(ro.__file__).parent), "impl": tag}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, (kind, B, T, H, U, P, K, C, dt) in TWIN_SHAPES.items():
+        dtype = getattr(torch, dt)
+        g = torch.Generator(device=device).manual_seed(7)
+        A = P ** U
+        q = torch.randn(B, T, H, U, P, device=device, generator=g).to(dtype)
+        k = torch.randn(B, T, H, U, P, device=device, generator=g).to(dtype)
+        E = H // 2
+        if kind == "addr":
+            pos = torch.arange(T, device=device).view(1, T).expand(B, T).contiguous()
+            view = k.permute(0, 2, 3, 4, 1)  # (B,H,U,P,T) view of token-major storage, as the attention layer has it
+
+            def call():
+                return ro.topk_addr(view, E, pos, K, 0.0, impl_backend="cuda")
+        else:
+            v = torch.randn(B, T, H, C, device=device, generator=g).to(dtype)
+            gm = torch.sigmoid(torch.randn(B, T, H, device=device, generator=g)).to(dtype)
+            if kind == "prefill":
+                def call():
+                    return ro.random_access_memory_attention(k, q, v, gm, embed_num=E, top_k=K, impl_backend="cuda")
+            else:
+                slot = torch.randn(B, H, A, C, device=device, generator=g) * 0.1
+                mass = torch.rand(B, H, A, device=device, generator=g) + 0.1
+                pos = torch.full((B, 1), 5, device=device)
+
+                def call():
+                    return ro.random_access_memory_attention(k, q, v, gm, (slot, mass), embed_num=E, position_ids=pos,
+                                                             top_k=K, inplace=True, impl_backend="cuda")
+        try:
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            reps = 20 if kind != "prefill" or B * T < 10000 else 5
+            times = []
+            for _ in range(3):
+                e0.record()
+                for _ in range(reps):
+                    call()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1) / reps)
+            out[name] = median(times)
+        except Exception as exc:  # noqa: BLE001
+            out[name] = f"failed: {type(exc).__name__}: {exc}"[:160]
+        del q, k
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_twin():
+    """ours in this process, the reference in a subprocess; returns the `twin` object of the JSON line."""
+    if not (TWIN_REF_DIR / "ramnet_ops").exists():
+        return {"unavailable": "reference ops package (with its built extension) not found under baseline/_ref/ops_pkg"}
+    ours = twin_times("ours")
+    env = dict(os.environ)
+    res = subprocess.run([sys.executable, str(Path(__file__).resolve()), "--twin-ref-worker"], capture_output=True, text=True,
+                         env=env, timeout=900)
+    try:
+        ref = json.loads(res.stdout.strip().splitlines()[-1])
+    except Exception:  # noqa: BLE001
+        return {"unavailable": "reference worker failed: " + (res.stderr or res.stdout)[-300:]}
+    twin = {"api": "ramnet_ops.random_access_memory_attention / topk_addr, impl_backend='cuda', CUDA events, median of 3",
+            "reference_package": ref.get("package"), "our_package": ours.get("package")}
+    for name in TWIN_SHAPES:
+        a, b = ref.get(name), ours.get(name)
+        twin[name] = {"reference_ms": a, "ours_ms": b,
+                      "speedup": (a / b) if isinstance(a, float) and isinstance(b, float) and b > 0 else None}
+    return twin
+
+
+# ---------------------------------------------------------------------------------------------
+# full language model (24 blocks, d_model 2048, 16 heads, U2 P64 K16 C128, SwiGLU 5632, vocab 32000), batch 64
+# sharded over the ranks: 2048-token prompt, then 512 greedy tokens.  The model classes are the reference's
+# (package `ramnet`, looked for on the import path and under baseline/_ref); the operators are this package's.
+# ---------------------------------------------------------------------------------------------
+def run_full_model(args, device, rank, world, barrier, max_over_ranks, dist):
+    ref_dir = ROOT / "baseline" / "_ref"
+    if ref_dir.exists() and str(ref_dir) not in sys.path:
+        sys.path.append(str(ref_dir))
+    try:
+        from ramnet.models import RAMNetConfig, RAMNetForCausalLM
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": f"reference model package `ramnet` not importable: {type(exc).__name__}: {exc}"[:200]}
+    from ramnet_ops.layers import GreedyGraphDecoder, use_fused_attention
+    B_total, T_prompt, n_new = 64, 2048, 512
+    B = max(1, B_total // world)
+    cfg = RAMNetConfig(hidden_size=2048, num_attention_heads=16, num_hidden_layers=24, addr_order=2, addr_radix=64,
+                       value_chs=128, embed_num=8, addr_top_k=16, hidden_act="SwiGLU", intermediate_size=5632,
+                       fuse_norm=False, fuse_cross_entropy=False, vocab_size=32000)
+    torch.manual_seed(1234)  # the same random-init weights on every rank
+    with torch.device(device):
+        model = RAMNetForCausalLM(cfg)
+    model = model.to(torch.bfloat16).eval()
+    g = torch.Generator(device=device).manual_seed(500 + rank)
+    ids = torch.randint(3, 32000, (B, T_prompt), device=device, generator=g)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def prompt(tokens):
+        with torch.no_grad():
+            out = model.model(input_ids=tokens, use_cache=True)
+            first = model.lm_head(out.last_hidden_state[:, -1]).argmax(-1, keepdim=True)
+        return out.past_key_values, first
+
+    prompt(ids[:1, :128])  # warm-up of kernels and GEMM heuristics
+    torch.cuda.synchronize()
+    barrier()
+    e0.record()
+    cache, first = prompt(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
+
+    # decode, the reference's own layer code step by step from Python, for a few tokens (the graph-replayed
+    # generation below continues from where these steps leave the state)
+    eager_steps = 16
+    tok = first
+    with torch.no_grad():
+        for i in range(eager_steps + 2):
+            if i == 2:
+                torch.cuda.synchronize()
+                e0.record()
+            out = model.model(input_ids=tok, past_key_values=cache, use_cache=True)
+            tok = model.lm_head(out.last_hidden_state[:, -1]).argmax(-1, keepdim=True)
+    e1.record()
+    torch.cuda.synchronize()
+    eager_ms = e0.elapsed_time(e1) / eager_steps
+    first = tok
+
+    # decode, fused one-token step replayed from a CUDA graph; the generated ids of all ranks are gathered (NCCL)
+    decoder = GreedyGraphDecoder(model, cache, first)
+    barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    new_ids = decoder.generate(n_new)
+    if dist is not None:
+        gathered = [torch.empty_like(new_ids) for _ in range(world)]
+        dist.all_gather(gathered, new_ids)
+        new_ids = torch.cat(gathered, dim=0)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    decode_ms = max_over_ranks(e0.elapsed_time(e1))
+    state_gb = sum(l.state.slot.numel() * 4 for l in (cache.get_layer(i) for i in range(len(cache)))) / 1e9
+    res = {"workload": f"full LM 24 x (d2048, H16, C128, U2 P64 K16, CAPE on 8 heads, SwiGLU 5632), vocab 32000, bf16 random init, "
+                       f"batch {B_total} sharded {B} per rank, {T_prompt}-token prompt + {n_new} greedy tokens",
+           "prefill_tokens_per_s": world * B * T_prompt / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+           "decode_tokens_per_s": world * B * n_new / (decode_ms / 1e3), "decode_ms_per_token_step": decode_ms / n_new,
+           "decode_ms_per_token_step_reference_layer_eager": eager_ms,
+           "state_gb_per_rank": state_gb, "gathered_ids_shape": list(new_ids.shape),
+           "collective": "all_gather of the generated ids (NCCL)" if dist is not None else "none (one rank)",
+           "model_classes": "reference `ramnet` package, attention switched to the fused one-token step for generation"}
+    del decoder, cache, model
+    torch.cuda.empty_cache()
+    return res
+
+
+# ---------------------------------------------------------------------------------------------
 # CPU baseline: the oracle port on a bounded sample of the prefill workload (and the parity check)
 # ---------------------------------------------------------------------------------------------
 def close_enough(got, want, atol, rtol, max_bad):
@@ -571,6 +750,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill"])
     ap.add_argument("--no-extra", action="store_true", help="skip the decode and address-only measurements")
+    ap.add_argument("--no-full-model", action="store_true", help="skip the full language-model run")
+    ap.add_argument("--no-twin", action="store_true", help="skip the twin-shape comparison with the reference's CUDA kernels")
+    ap.add_argument("--twin-ref-worker", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--ncu-case", default=None, choices=["prefill_small", "decode_small", "addr_small"],
                     help="run one small case of the kernels (for profiler captures) and exit")
     args = ap.parse_args()
@@ -582,6 +764,10 @@ def main():
 
     if args.ncu_case:
         run_ncu_case(args.ncu_case)
+        return
+    if args.twin_ref_worker:  # subprocess of run_twin(): the REFERENCE package has to win the import
+        sys.path.insert(0, str(TWIN_REF_DIR))
+        emit(twin_times("reference"))
         return
 
     if args.impl == "reference":
@@ -634,6 +820,9 @@ def main():
         a = run_addr(args, device, rank, barrier, max_over_ranks)
         extra = {"decode": d, "addr": a}
         torch.cuda.empty_cache()
+        if not args.no_full_model:
+            extra["full_model"] = run_full_model(args, device, rank, world, barrier, max_over_ranks, dist)
+            torch.cuda.empty_cache()
         if world > 1:
             # the benchmark batch split over the ranks (strong scaling): prefill B = 8 / N, decode batch 256 / N
             sp = run_prefill(args, device, rank, barrier, max_over_ranks, batch=max(1, SHAPES["prefill"]["B"] // world), full=False)
@@ -690,6 +879,10 @@ def main():
         line["addr"] = {"tokens_per_s": world * a["tokens_per_s"], "kernel_ms": a["kernel_ms"], "achieved_gbs": a["kernel_gbs"],
                         "frac": a["kernel_gbs"] / peak, "algorithmic_bytes": a["bytes"],
                         "workload": "addr B8 T8192 H16 U3 P32 K8 bf16"}
+        if "full_model" in extra:
+            line["full_model"] = extra["full_model"]
+        if rank == 0 and world == 1 and not args.no_twin:
+            line["twin"] = run_twin()
         if "strong" in extra:
             sp, sd = extra["strong"]
             sp_ms = median(sp["regions_ms"]) / sp["passes"]

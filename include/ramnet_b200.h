@@ -160,6 +160,11 @@ int64_t rn_gsu_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64
  * rn_gsu_owner_enable), which keeps the state of a (batch, head) in the shared memory of one 16-CTA cluster and
  * needs NO workspace: the answer is then 0 and rn_gsu_fwd accepts workspace == NULL.
  * rn_gsu_workspace_bytes() is always sufficient. */
+/* Which kernels rn_gsu_fwd runs for a shape (no counterpart in the reference): 0 general apply kernel, 1 channel-slice
+ * kernels with per-slot chains, 2 slot-owner cluster kernel; -1 on invalid dimensions.  rows_aligned as in
+ * rn_gsu_fwd_workspace_bytes. */
+int rn_gsu_fwd_path(int dtype, int rows_aligned, int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw,
+                    int64_t Kr, int device);
 /* The slot-owner kernel is an alternative forward path, off by default (on B200 the channel-slice kernels are
  * faster); rn_gsu_owner_enable(1) switches it on for the process, returns the previous setting (-1 = never set,
  * then the environment variable RN_PREFILL_OWNER=1 decides).  rn_gsu_owner_profile() hands it a device buffer

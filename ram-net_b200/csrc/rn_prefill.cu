@@ -782,6 +782,17 @@ extern "C" int64_t rn_gsu_fwd_workspace_bytes(int dtype, int rows_aligned, int64
     return int64_t(pl.total);
 }
 
+// Which forward path rn_gsu_fwd takes for a shape: 0 general apply kernel, 1 channel-slice kernels with per-slot chains,
+// 2 slot-owner cluster kernel.  rows_aligned: x / y rows start on 16-byte boundaries.
+extern "C" int rn_gsu_fwd_path(int dtype, int rows_aligned, int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw,
+                               int64_t Kr, int device) {
+    rn_clear_error();
+    RnGsuPlan pl;
+    if (rn_gsu_plan(B, H, T, A, C, Kw, Kr, device, &pl)) return -1;
+    if (rn_gsu_fwd_workspace_bytes(dtype, rows_aligned, B, H, T, A, C, Kw, Kr, device) == 0) return 2;
+    return (pl.fast && rows_aligned) ? 1 : 0;
+}
+
 template <typename T, bool SMEM>
 static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int bh = p.B * p.H;

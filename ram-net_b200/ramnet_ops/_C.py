@@ -43,6 +43,8 @@ lib.rn_gsu_workspace_bytes.restype = ctypes.c_int64
 lib.rn_gsu_workspace_bytes.argtypes = [_i64] * 7 + [_i32]
 lib.rn_gsu_fwd_workspace_bytes.restype = ctypes.c_int64
 lib.rn_gsu_fwd_workspace_bytes.argtypes = [_i32, _i32] + [_i64] * 7 + [_i32]
+lib.rn_gsu_fwd_path.restype = ctypes.c_int
+lib.rn_gsu_fwd_path.argtypes = [_i32, _i32] + [_i64] * 7 + [_i32]
 lib.rn_gsu_owner_enable.restype = ctypes.c_int
 lib.rn_gsu_owner_enable.argtypes = [_i32]
 lib.rn_gsu_owner_profile.restype = ctypes.c_int
@@ -111,6 +113,8 @@ def gsu_plan_info(B, H, T, A, C, Kw, Kr, reverse=False, device=0) -> dict:
     # forward of 16-bit values with 16-byte aligned rows: 1 when the slot-owner cluster kernel takes the call
     # (it needs no workspace), 0 when the channel-slice kernels do
     info["owner_16bit"] = int(lib.rn_gsu_fwd_workspace_bytes(DTYPE_CODE[torch.bfloat16], 1, B, H, T, A, C, Kw, Kr, device) == 0)
+    # 0 general, 1 channel-slice kernels with chains, 2 slot-owner cluster kernel
+    info["fwd_path_16bit"] = int(lib.rn_gsu_fwd_path(DTYPE_CODE[torch.bfloat16], 1, B, H, T, A, C, Kw, Kr, device))
     return info
 
 

@@ -23,6 +23,8 @@ SHAPES = [
     (1, 2, 2, 3, 6, 9, 1, torch.float32, 1.0),
     (1, 2, 1, 40, 6, 5, 1, torch.float32, 1.0),
     (1, 1, 2, 100, 4, 64, 0, torch.bfloat16, 2.0),
+    (2, 4, 5, 8, 40, 8, 2, torch.bfloat16, 1.5),     # 32768 slots at radix 8: thread-per-row kernel
+    (1, 2, 5, 8, 20, 8, 1, torch.float32, 1.0),
 ]
 
 

@@ -129,16 +129,19 @@ def test_ram_gradients_oracle_matches_reference(name):
 def test_epilogue_restatement_equals_torch_rmsnorm_and_sigmoid():
     """head_rmsnorm_gate restates the layer epilogue of the reference
     (packages/ramnet/src/ramnet/layers/ram_attn_block.py:142-143,342-348): torch.nn.RMSNorm over the C channels
-    of every head with eps=None (finfo(dtype).eps), times Sigmoid(gate logits).  Pinned against those modules."""
+    of every head with eps=None, times Sigmoid(gate logits).  Pinned against those modules, with small inputs so
+    that the epsilon matters: eps=None means the epsilon of the type torch computes the norm in, float32 for
+    bfloat16 inputs too (not finfo(bfloat16).eps)."""
     g = torch.Generator().manual_seed(0)
     for dtype in (torch.float32, torch.bfloat16):
-        B, T, H, C = 2, 3, 4, 32
-        y = torch.randn(B, T, H, C, generator=g).to(dtype)
-        gate_logits = torch.randn(B, T, H, C, generator=g).to(dtype)
-        norm = torch.nn.RMSNorm(C, eps=None, dtype=dtype)
-        with torch.no_grad():
-            norm.weight.copy_((torch.randn(C, generator=g) * 0.1 + 1.0).to(dtype))
-            want = norm(y) * torch.nn.Sigmoid()(gate_logits)
-        got = orc.head_rmsnorm_gate(y.float(), norm.weight.float(), gate_logits.float(), float(torch.finfo(dtype).eps))
-        tol = 1e-6 if dtype == torch.float32 else 2e-2
-        torch.testing.assert_close(got, want.float(), atol=tol, rtol=tol)
+        for scale in (1.0, 1e-3):
+            B, T, H, C = 2, 3, 4, 32
+            y = (torch.randn(B, T, H, C, generator=g) * scale).to(dtype)
+            gate_logits = torch.randn(B, T, H, C, generator=g).to(dtype)
+            norm = torch.nn.RMSNorm(C, eps=None, dtype=dtype)
+            with torch.no_grad():
+                norm.weight.copy_((torch.randn(C, generator=g) * 0.1 + 1.0).to(dtype))
+                want = norm(y) * torch.nn.Sigmoid()(gate_logits)
+            got = orc.head_rmsnorm_gate(y.float(), norm.weight.float(), gate_logits.float(), float(torch.finfo(torch.float32).eps))
+            tol = 1e-5 if dtype == torch.float32 else 3e-2
+            torch.testing.assert_close(got, want.float(), atol=tol, rtol=tol)
