@@ -426,8 +426,10 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_apply_kernel(const RnGs
 // owners.  Two CTA barriers per chunk; the records are double buffered by 1-D bulk copies and only
 // one thread polls the copy's mbarrier.
 // ------------------------------------------------------------------------------------------
-template <typename T, int CS, int EV>
-__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2) {
+// MODEL: the instance for Kw = Kr = 16 with 64-token chunks (2048 events, 16 threads per token): these are then
+// compile-time constants, so the index arithmetic of the event loops folds into shifts.
+template <typename T, int CS, int EV, bool MODEL = false>
+__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(const RnGsuParams p, const int tpt_log2_) {
     constexpr int G = CS / 4;  // threads per event (one float4 of channels each)
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ __align__(8) uint64_t mbar[2];
@@ -436,10 +438,13 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     const int bh = blockIdx.x / p.nslices;
     const int b = bh / p.H, h = bh % p.H;
     const int tid = threadIdx.x;
-    const int C = p.C, A = p.A, Kw = p.Kw, Kr = p.Kr, KT = p.Kw + p.Kr, L = p.L;
+    const int C = p.C, A = p.A;
+    const int Kw = MODEL ? 16 : p.Kw, Kr = MODEL ? 16 : p.Kr, KT = MODEL ? 32 : p.Kw + p.Kr, L = MODEL ? 64 : p.L;
+    const int NEp = MODEL ? 2048 : p.NEp;
+    const int tpt_log2 = MODEL ? 4 : tpt_log2_;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);  // multiple of 4
-    const uint32_t rec_copy = uint32_t(size_t(p.NEp) * 9 + 16);  // {coef, link}[NEp], heads[8 + NEp/2]
+    const uint32_t rec_copy = uint32_t(size_t(NEp) * 9 + 16);  // {coef, link}[NEp], heads[8 + NEp/2]
     const uint32_t kt_magic = 0xffffffffu / uint32_t(KT) + 1u;  // e / KT == __umulhi(e, kt_magic) for e < 4096
 
     // thread -> (token of the chunk, k-lane, channel group)
@@ -464,7 +469,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     }
     __syncthreads();
     // the part of a chunk record this kernel reads: the {coef, link} pairs and the head list, contiguous
-    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes + RN_GSU_HDR_BYTES + size_t(p.NEp) * 8;
+    const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes + RN_GSU_HDR_BYTES + size_t(NEp) * 8;
     auto fetch = [&](int chunk) {  // one thread; the target buffer was last read before a CTA barrier
         uint64_t *bar = &mbar[chunk & 1];
         rn_mbar_expect_tx(bar, rec_copy);
@@ -512,7 +517,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
         xnext = load_x(chunk + 1);
         const unsigned char *rec = rec0 + (chunk & 1) * rec_stride;
         const uint2 *e_pair = reinterpret_cast<const uint2 *>(rec);
-        const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(p.NEp) * 8);
+        const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(NEp) * 8);
 
         // ---- first events, token-major: records, then rows, then arithmetic, then stores ------------------
         if (q == 0 && tok < L) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
@@ -812,6 +817,12 @@ static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStr
 template <typename T>
 static int rn_launch_apply_fast(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int grid = p.B * p.H * pl.nslices;
+    if (pl.cs == 8 && pl.ev == 4 && p.Kw == 16 && p.Kr == 16 && pl.L == 64 && pl.NEp == 2048 && pl.tpt_log2 == 4) {
+        RN_CUDA(cudaFuncSetAttribute(rn_gsu_apply_fast_kernel<T, 8, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(pl.apply_smem)));
+        rn_gsu_apply_fast_kernel<T, 8, 4, true><<<grid, RN_APPLY_THREADS, pl.apply_smem, stream>>>(p, pl.tpt_log2);
+        return 0;
+    }
 #define RN_CASE(CSV, EVV)                                                                                       \
     if (pl.cs == CSV && pl.ev == EVV) {                                                                         \
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_apply_fast_kernel<T, CSV, EVV>,                                     \

@@ -50,8 +50,9 @@ __device__ __forceinline__ float rn_group_sum(float v, int G, unsigned mask) {
 //            read:  d_r += <slot, d_y>   (float atomics across the channel slices)
 //   reverse  read:  d_slot += r * d_y
 //            write: d_gain += <d_slot, delta>, d_x += gain * d_slot, d_slot *= 1 - gain
-template <typename T, int CS, int EV, bool REVERSE>
-__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2) {
+// MODEL: the instance for Kw = Kr = 16 with 64-token chunks (see rn_gsu_apply_fast_kernel)
+template <typename T, int CS, int EV, bool REVERSE, bool MODEL = false>
+__global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2_) {
     constexpr int G = CS / 4;
     const RnGsuParams &p = bp.f;
     extern __shared__ __align__(16) unsigned char dyn[];
@@ -61,10 +62,12 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     const int bh = blockIdx.x / p.nslices;
     const int b = bh / p.H, h = bh % p.H;
     const int tid = threadIdx.x, lane = tid & 31;
-    const int C = p.C, A = p.A, Kw = p.Kw, KT = p.Kw + p.Kr, L = p.L;
+    const int C = p.C, A = p.A;
+    const int Kw = MODEL ? 16 : p.Kw, KT = MODEL ? 32 : p.Kw + p.Kr, L = MODEL ? 64 : p.L, NEp = MODEL ? 2048 : p.NEp;
+    const int tpt_log2 = MODEL ? 4 : tpt_log2_;
     const int c0 = slice * CS;
     const int cvalid = min(CS, C - c0);
-    const uint32_t rec_copy = uint32_t(size_t(p.NEp) * 9 + 16);  // {coef, link}[NEp], heads[8 + NEp/2]
+    const uint32_t rec_copy = uint32_t(size_t(NEp) * 9 + 16);  // {coef, link}[NEp], heads[8 + NEp/2]
     const uint32_t kt_magic = 0xffffffffu / uint32_t(KT) + 1u;  // e / KT == __umulhi(e, kt_magic) for e < 4096
 
     const int TPT = 1 << tpt_log2;
@@ -91,7 +94,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     __syncthreads();
     // forward sweeps read the pairs / heads built for time order, the reverse sweep their mirror image
     const unsigned char *records = p.records + int64_t(bh) * p.nchunks * p.rec_bytes + RN_GSU_HDR_BYTES +
-                                   size_t(p.NEp) * (REVERSE ? 17 : 8) + (REVERSE ? 16 : 0);
+                                   size_t(NEp) * (REVERSE ? 17 : 8) + (REVERSE ? 16 : 0);
     const int first = REVERSE ? p.nchunks - 1 : 0;
     const int step = REVERSE ? -1 : 1;
     auto fetch = [&](int it, int chunk) {  // one thread; the target buffer was last read before a CTA barrier
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
         dynext = load_row(dy, bp.dyt, more ? chunk + step : -1);
         const unsigned char *rec = rec0 + (it & 1) * rec_stride;
         const uint2 *e_pair = reinterpret_cast<const uint2 *>(rec);
-        const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(p.NEp) * 8);
+        const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(NEp) * 8);
         // per-write-event rows in the workspaces: index of (t, k) = (bh*T + t)*Kw + k
         const int64_t wchunk = (int64_t(bh) * p.T + t0) * Kw;
         const int64_t wbase = wchunk + int64_t(tok) * Kw;
@@ -525,6 +528,12 @@ static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaSt
     if (smem > 227 * 1024) {
         rn_set_error("backward sweep needs %zu bytes of shared memory", smem);
         return 1;
+    }
+    if (pl.cs == 8 && pl.ev == 4 && bp.f.Kw == 16 && bp.f.Kr == 16 && pl.L == 64 && pl.NEp == 2048 && pl.tpt_log2 == 4) {
+        RN_CUDA(cudaFuncSetAttribute(rn_gsu_bwd_sweep_kernel<T, 8, 4, REVERSE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(smem)));
+        rn_gsu_bwd_sweep_kernel<T, 8, 4, REVERSE, true><<<grid, RN_APPLY_THREADS, smem, stream>>>(bp, pl.tpt_log2);
+        return 0;
     }
 #define RN_CASE(CSV, EVV)                                                                                            \
     if (pl.cs == CSV && pl.ev == EVV) {                                                                               \

