@@ -453,7 +453,9 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
     const int tok = tid >> tpt_log2;        // tokens >= L (surplus threads) take no token-major work
     const int w = tid & (TPT - 1);
     const int sub = w % G, q = w / G;
-    const bool chan_ok = sub * 4 < cvalid;
+    const bool chan_ok = MODEL || sub * 4 < cvalid;  // MODEL: C is a multiple of the slice width
+    // is this thread's j-th event a write?  MODEL: 8 k-lanes per token, so events 0, 1 are writes and 2, 3 reads
+    auto wr_of = [&](int j) { return MODEL ? (j < 2) : (q + j * KL < Kw); };
 
     // dynamic smem: rec[2][rec_stride] | S[A*CS] | xt[L*CS] | ylate[L*Kr*CS]
     const size_t rec_stride = (size_t(rec_copy) + 127) / 128 * 128;
@@ -532,14 +534,14 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
             for (int i = 0; i < NB; ++i) {
                 const int k = q + (jb + i) * KL;
                 pr[i] = make_uint2(0u, RN_LINK_DEAD);
-                if (tok_ok && k < KT) pr[i] = e_pair[tok * KT + k];
+                if (tok_ok && (MODEL || k < KT)) pr[i] = e_pair[tok * KT + k];
             }
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
                 const uint32_t kind = (pr[i].y >> RN_LINK_KIND_SHIFT) & 7u;  // bit 2: dead
                 if (kind < RN_KIND_HEAD) {
                     row[i] = *reinterpret_cast<const float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4);
-                } else if (kind <= RN_KIND_LATER && q + (jb + i) * KL >= Kw) {
+                } else if (kind <= RN_KIND_LATER && !wr_of(jb + i)) {
                     late |= 1u << (jb + i);
                 }
             }
@@ -547,7 +549,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_apply_fast_kernel(
             for (int i = 0; i < NB; ++i) {
                 if (((pr[i].y >> RN_LINK_KIND_SHIFT) & 7u) >= RN_KIND_HEAD) continue;
                 const float cf = __uint_as_float(pr[i].x);
-                if (q + (jb + i) * KL < Kw) {
+                if (wr_of(jb + i)) {
                     float4 s = row[i];
                     s.x = fmaf(cf, xv.x - s.x, s.x);
                     s.y = fmaf(cf, xv.y - s.y, s.y);
@@ -817,7 +819,7 @@ static int rn_launch_schedule(const RnGsuParams &p, const RnGsuPlan &pl, cudaStr
 template <typename T>
 static int rn_launch_apply_fast(const RnGsuParams &p, const RnGsuPlan &pl, cudaStream_t stream) {
     const int grid = p.B * p.H * pl.nslices;
-    if (pl.cs == 8 && pl.ev == 4 && p.Kw == 16 && p.Kr == 16 && pl.L == 64 && pl.NEp == 2048 && pl.tpt_log2 == 4) {
+    if (pl.cs == 8 && pl.ev == 4 && p.Kw == 16 && p.Kr == 16 && pl.L == 64 && pl.NEp == 2048 && pl.tpt_log2 == 4 && p.C % 8 == 0) {
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_apply_fast_kernel<T, 8, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(pl.apply_smem)));
         rn_gsu_apply_fast_kernel<T, 8, 4, true><<<grid, RN_APPLY_THREADS, pl.apply_smem, stream>>>(p, pl.tpt_log2);

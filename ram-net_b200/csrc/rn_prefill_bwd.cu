@@ -75,7 +75,9 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     const int tok = tid >> tpt_log2;
     const int w = tid & (TPT - 1);
     const int sub = w % G, q = w / G;
-    const bool chan_ok = sub * 4 < cvalid;
+    const bool chan_ok = MODEL || sub * 4 < cvalid;  // MODEL: C is a multiple of the slice width
+    // is this thread's j-th event a write?  MODEL: 8 k-lanes per token, so events 0, 1 are writes and 2, 3 reads
+    auto wr_of = [&](int j) { return MODEL ? (j < 2) : (q + j * KL < Kw); };
     const unsigned gmask = (G >= 32 ? 0xffffffffu : ((1u << G) - 1u)) << (lane & ~(G - 1));  // the lanes of one event
 
     // dynamic smem: rec[2][rec_stride] | S[A*CS] | xt[L*CS] (replay) | dyt[L*CS] | dxlate[L*Kw*CS] (reverse)
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
             for (int i = 0; i < NB; ++i) {
                 const int k = q + (jb + i) * KL;
                 pr[i] = make_uint2(0u, RN_LINK_DEAD);
-                if (tok_ok && k < KT) pr[i] = e_pair[tok * KT + k];
+                if (tok_ok && (MODEL || k < KT)) pr[i] = e_pair[tok * KT + k];
             }
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
@@ -175,8 +177,8 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                 dl[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (kind < RN_KIND_HEAD) {
                     row[i] = *reinterpret_cast<const float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4);
-                    if (REVERSE && k < Kw && chan_ok) dl[i] = *reinterpret_cast<const float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4);
-                } else if (REVERSE && kind <= RN_KIND_LATER && k < Kw) {
+                    if (REVERSE && wr_of(jb + i) && chan_ok) dl[i] = *reinterpret_cast<const float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4);
+                } else if (REVERSE && kind <= RN_KIND_LATER && wr_of(jb + i)) {
                     late |= 1u << (jb + i);
                 }
             }
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                 float *dst = S + (pr[i].y & 0xffffu) * CS + sub * 4;
                 float4 s = row[i];
                 if (!REVERSE) {
-                    if (k < Kw) {
+                    if (wr_of(jb + i)) {
                         const float4 d = make_float4(xv.x - s.x, xv.y - s.y, xv.z - s.z, xv.w - s.w);
                         if (chan_ok) *reinterpret_cast<float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4) = d;
                         s.x = fmaf(cf, d.x, s.x);
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                         if (sub == 0) atomicAdd(bp.dval + b * bp.vb + h * bp.vh + int64_t(k) * bp.vk + int64_t(t0 + tok) * bp.vt, dot);
                     }
                 } else {
-                    if (k >= Kw) {
+                    if (!wr_of(jb + i)) {
                         s.x = fmaf(cf, dyv.x, s.x);
                         s.y = fmaf(cf, dyv.y, s.y);
                         s.z = fmaf(cf, dyv.z, s.z);
@@ -529,7 +531,7 @@ static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaSt
         rn_set_error("backward sweep needs %zu bytes of shared memory", smem);
         return 1;
     }
-    if (pl.cs == 8 && pl.ev == 4 && bp.f.Kw == 16 && bp.f.Kr == 16 && pl.L == 64 && pl.NEp == 2048 && pl.tpt_log2 == 4) {
+    if (pl.cs == 8 && pl.ev == 4 && bp.f.Kw == 16 && bp.f.Kr == 16 && pl.L == 64 && pl.NEp == 2048 && pl.tpt_log2 == 4 && bp.f.C % 8 == 0) {
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_bwd_sweep_kernel<T, 8, 4, REVERSE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      int(smem)));
         rn_gsu_bwd_sweep_kernel<T, 8, 4, REVERSE, true><<<grid, RN_APPLY_THREADS, smem, stream>>>(bp, pl.tpt_log2);

@@ -6,10 +6,11 @@ module captures ``n`` consecutive steps -- the fused decode operator on static i
 on-device increment of the position counter -- into one CUDA graph that is replayed with one launch.
 
 It plays the role of the static-state decode loop of the reference's cache
-(packages/ramnet/src/ramnet/cache.py: ``RAMCache.update`` keeps ``slot``/``mass`` in place and a
-``next_position`` counter; packages/ramnet/src/ramnet/ram_attn_block.py:342-350 calls the in-place
-operator once per token): the slot and mass tensors are updated in place, the position lives on the
-device, and the caller only refreshes the input buffers between replays.
+(packages/ramnet/src/ramnet/layers/cache.py:33-50,123-130: ``RAMCache.update`` keeps ``slot``/``mass`` and a
+``next_position`` counter per layer; packages/ramnet/src/ramnet/layers/ram_attn_block.py:324-350 calls the
+in-place operator once per token and then the layer epilogue): the slot and mass tensors are updated in place,
+the position lives on the device, and the caller only refreshes the input buffers between replays.  For a whole
+model see ``ramnet_ops.layers.GreedyGraphDecoder``.
 """
 from __future__ import annotations
 
