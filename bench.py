@@ -683,8 +683,9 @@ def run_ncu_case(name):
     device = torch.device("cuda", 0)
     ops = torch.ops.ramnet_ops
     g = torch.Generator(device=device).manual_seed(0)
-    if name == "prefill_small":
-        B, T, H, U, P, K, C, E = 2, 4096, 16, 2, 64, 16, 128, 8
+    if name in ("prefill_small", "prefill_full"):
+        # prefill_full: the benchmark shape itself, three passes (for the one-pass launch list only)
+        B, T, H, U, P, K, C, E = (2, 4096, 16, 2, 64, 16, 128, 8) if name == "prefill_small" else (8, 16384, 16, 2, 64, 16, 128, 8)
         A = P ** U
         q = torch.randn(B, T, H, U, P, device=device, generator=g).bfloat16()
         k = torch.randn(B, T, H, U, P, device=device, generator=g).bfloat16()
@@ -753,7 +754,7 @@ def main():
     ap.add_argument("--no-full-model", action="store_true", help="skip the full language-model run")
     ap.add_argument("--no-twin", action="store_true", help="skip the twin-shape comparison with the reference's CUDA kernels")
     ap.add_argument("--twin-ref-worker", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--ncu-case", default=None, choices=["prefill_small", "decode_small", "addr_small"],
+    ap.add_argument("--ncu-case", default=None, choices=["prefill_small", "prefill_full", "decode_small", "addr_small"],
                     help="run one small case of the kernels (for profiler captures) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -914,7 +915,7 @@ def main():
 # case, per (b,t,h), to be scaled to the benchmark shape by the token-heads processed (the traffic is x / y rows,
 # decoded addresses and the state round trip, all proportional to them at fixed T).  None: no capture yet.
 TRAFFIC = {
-    "rn_gsu_apply_fast_kernel": {"bytes_per_bth": (139.404544e6 + 69.276672e6) / (2 * 4096 * 16),
+    "rn_gsu_apply_fast_kernel": {"bytes_per_bth": (139.20384e6 + 63.06048e6) / (2 * 4096 * 16),
                                  "capture": "ncu, --ncu-case prefill_small (B2 T4096 H16), scaled by token-heads"},
 }
 
