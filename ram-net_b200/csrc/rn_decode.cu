@@ -418,22 +418,25 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
 // ------------------------------------------------------------------------------------------
 // The two halves of a warp decode the write and the read address of the pair with the
 // sixteen-lanes-per-row decoder (rn_addr_half.cuh; a dependent chain of ~2 us instead of ~14 us),
-// then the same warp moves the rows: the 16 write rows by 1-D bulk async copies through its
-// shared-memory buffer (global -> shared, update, shared -> global), the 16 read rows by per-lane
-// loads into registers at the same time; a read row that is also written in this step is taken
-// from the updated copy in shared memory.  Warps are independent (no CTA barrier), so the address
+// then the same warp moves the rows, all by 1-D bulk async copies through its shared-memory buffer: the 16
+// write rows (global -> shared, update, shared -> global), then, into the same buffer, the 16 read rows; a read
+// row that is also written in this step is taken from the updated copy before the buffer is reused.  Warps are independent (no CTA barrier), so the address
 // decode of some pairs overlaps the row traffic of others; a CTA's warps walk the pairs with a
 // grid-wide stride.
-constexpr int RN_DECP_THREADS = 256;
+// Warps per CTA: with C = 128 a warp needs 8 KB of shared memory (its 16 write rows) and the kernel fits 72 registers
+// (the read rows stream through registers four at a time), so two CTAs of 14 warps are resident per SM: 28 warps,
+// one for each of the 27.7 (b,h) pairs an SM gets at batch 256 x 16 heads, and no pair waits for a second round.
+template <int NV> struct RnDecPair { static constexpr int THREADS = NV == 1 ? 448 : 256; };
 
 template <typename T, int NV>
-__device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
-                                                    const int which, const uint32_t cand, const uint2 (&logits)[2],
-                                                    float *wbuf, uint64_t *bar, uint32_t &phase);
+__device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
+                                                        const int which, const uint32_t cand, const uint2 (&logits)[2],
+                                                        float *wbuf, uint64_t *bar, uint32_t phase);
 
 template <typename T, int NV>
-__global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(const RnDecodeParams p) {
+__global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kernel(const RnDecodeParams p) {
     constexpr int U = 2, P = 64, K = 16;
+    constexpr int RN_DECP_THREADS = RnDecPair<NV>::THREADS;
     extern __shared__ __align__(128) unsigned char row_bytes_buf[];  // per warp: K rows of C floats
     __shared__ __align__(8) uint64_t mbar[RN_DECP_THREADS / 32];
 
@@ -469,7 +472,7 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
         // the logits of the following pair are requested now and used after this pair is done
         uint2 logits_next[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
         if (following < last) rn_half::load_logits<T>(logit_base + int64_t(following) * U * P, lane, logits_next);
-        rn_decode_pair_task<T, NV>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
+        phase = rn_decode_pair_task<T, NV>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
         if (phase & 2u) {  // a bulk copy never completed: the pair this warp had already drawn gets a zero output
             if (following < last) {
                 T *yr = static_cast<T *>(p.y) + int64_t(following) * (NV * 128);
@@ -484,11 +487,11 @@ __global__ void __launch_bounds__(RN_DECP_THREADS, 2) rn_decode_pair_kernel(cons
     }
 }
 
-// One (b,h) pair on one warp; phase bit 0 = parity of the warp's mbarrier, bit 1 = failure.
+// One (b,h) pair on one warp; phase bit 0 = parity of the warp's mbarrier, bit 1 = failure (returned).
 template <typename T, int NV>
-__device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
-                                                    const int which, const uint32_t cand, const uint2 (&logits)[2],
-                                                    float *wbuf, uint64_t *bar, uint32_t &phase) {
+__device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
+                                                        const int which, const uint32_t cand, const uint2 (&logits)[2],
+                                                        float *wbuf, uint64_t *bar, uint32_t phase) {
     constexpr int U = 2, P = 64, K = 16;
     constexpr int C = NV * 128;
     constexpr uint32_t ROW_BYTES = C * 4;
@@ -498,7 +501,7 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
         if (p.mask != nullptr && p.mask[b] == 0) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
-            return;
+            return phase;
         }
         float *slot = p.slot + int64_t(bh) * p.A * C;
         float *mass = p.mass + int64_t(bh) * p.A;
@@ -522,24 +525,11 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
         float r_l = __shfl_down_sync(RN_FULL, weight, 16);
         if (lane >= K) r_l = 0.f;
 
-        // ---- write rows: bulk copies into this warp's buffer -------------------------------------------
+        // ---- the rows, in two stages through this warp's buffer: the 16 write rows, then the 16 read rows ----
+        // One loop body for both stages on purpose: it holds the only wait of the task (two separate bounded waits
+        // in one task make ptxas 12.9 fail to allocate registers).
         const bool live_w = lane < K && w_l != 0.f;
         const float mass_l = live_w ? mass[a_l] : 0.f;  // requested before the row traffic
-        const int nlive = __popc(__ballot_sync(RN_FULL, live_w));
-        if (nlive > 0) {
-            if (lane == 0) rn_mbar_expect_tx(bar, uint32_t(nlive) * ROW_BYTES);
-            __syncwarp();
-            if (live_w) rn_bulk_g2s(wbuf + lane * C, slot + int64_t(a_l) * C, ROW_BYTES, bar);
-        }
-
-        // ---- read rows: per-lane loads into registers, in flight together with the bulk copies -------------
-        float4 rows[K][NV];
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-            const int a = __shfl_sync(RN_FULL, ar_l, k);
-#pragma unroll
-            for (int v = 0; v < NV; ++v) rows[k][v] = *reinterpret_cast<const float4 *>(slot + int64_t(a) * C + v * 128 + lane * 4);
-        }
         // a read row that this step also writes: index of that write row, else -1.  All 32 lanes hold a slot
         // (lower half write, upper half read): one match finds the equal ones.
         const unsigned live_mask = __ballot_sync(RN_FULL, live_w);
@@ -552,82 +542,125 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
             gain_l = g.gain;
             mass_new = g.mass;
         }
-        __syncwarp();
-        float4 xv[NV];
+        float4 xv[NV], acc[NV];
 #pragma unroll
-        for (int v = 0; v < NV; ++v) xv[v] = rn_cvt_raw4(xraw[v]);
-
-        bool landed = true;
-        if (nlive > 0) {
-            landed = rn_mbar_wait_bounded(bar, phase & 1u);
-            phase ^= 1u;
+        for (int v = 0; v < NV; ++v) {
+            xv[v] = rn_cvt_raw4(xraw[v]);
+            acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (!__all_sync(RN_FULL, landed)) {
-            // A bulk copy never completed: report it through the status word, leave slot AND mass of this
-            // pair as they were, give it a defined (zero) output and stop using the buffer (the copy may
-            // still land).
-            if (lane == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
-#pragma unroll
-            for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
-            phase |= 2u;
-            return;
-        }
-        if (live_w) mass[a_l] = mass_new;  // only once the rows are here: slot and mass move together
-        // four rows at a time: their loads are issued before the first store (the compiler cannot reorder them
-        // itself, loads and stores go to the same buffer)
-#pragma unroll
-        for (int k0 = 0; k0 < K; k0 += 4) {
-            float4 cur[4][NV];
-            float gain[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                gain[i] = __shfl_sync(RN_FULL, gain_l, k0 + i);
-#pragma unroll
-                for (int v = 0; v < NV; ++v) cur[i][v] = *reinterpret_cast<const float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (!(live_mask & (1u << (k0 + i)))) continue;  // not loaded: the buffer holds stale rows there
-#pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    float4 s = cur[i][v];
-                    s.x = fmaf(gain[i], xv[v].x - s.x, s.x);
-                    s.y = fmaf(gain[i], xv[v].y - s.y, s.y);
-                    s.z = fmaf(gain[i], xv[v].z - s.z, s.z);
-                    s.w = fmaf(gain[i], xv[v].w - s.w, s.w);
-                    *reinterpret_cast<float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4) = s;
-                }
-            }
-        }
-        rn_fence_proxy_async();  // the updated rows are read by the bulk copy engine next
-        __syncwarp();
-        if (live_w) rn_bulk_s2g(slot + int64_t(a_l) * C, wbuf + lane * C, ROW_BYTES);
-        rn_bulk_commit();
-
-        // ---- reads (after the writes of this step) ---------------------------------------------------
-        float4 acc[NV];
-#pragma unroll
-        for (int v = 0; v < NV; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
         float scale = 1.f;
-        if (p.mass_aware) {
-            const float rm = (lane < K && r_l != 0.f) ? r_l * mass[ar_l] : 0.f;
-            const float sr = rn_warp_sum(lane < K ? r_l : 0.f), srm = rn_warp_sum(rm);
-            scale = sr / (srm + p.eps);
-            r_l = rm;
-        }
+        bool want = live_w;        // this lane fetches a row in the current stage ...
+        int row = a_l;             // ... this one
+        float coef_l = gain_l;     // and lane k < 16 holds the coefficient of row k (gain, then read weight)
+#pragma unroll 1
+        for (int stage = 0; stage < 2; ++stage) {
+            const unsigned rows = __ballot_sync(RN_FULL, want);
+            bool landed = true;
+            if (rows != 0u) {
+                if (lane == 0) rn_mbar_expect_tx(bar, uint32_t(__popc(rows)) * ROW_BYTES);
+                __syncwarp();
+                if (want) rn_bulk_g2s(wbuf + lane * C, slot + int64_t(row) * C, ROW_BYTES, bar);
+                landed = rn_mbar_wait_bounded(bar, phase & 1u);
+                phase ^= 1u;
+            }
+            if (!__all_sync(RN_FULL, landed)) {
+                // A bulk copy never completed: report it through the status word and give the pair a defined (zero)
+                // output.  In the first stage slot AND mass of the pair stay as they were; in the second the state
+                // is already updated and only the output is lost.  The buffer is not used again (the copy may
+                // still land).
+                if (lane == 0) atomicMax(p.status, RN_STATUS_WAIT_TIMEOUT);
 #pragma unroll
-        for (int k = K - 1; k >= 0; --k) {
-            const float coef = __shfl_sync(RN_FULL, r_l, k);
-            const int al = __shfl_sync(RN_FULL, alias_l, k);
-            if (coef != 0.f) {
+                for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+                return phase | 2u;
+            }
+            if (stage == 0) {
+                if (live_w) mass[a_l] = mass_new;  // only once the rows are here: slot and mass move together
+                // four rows at a time: their loads are issued before the first store (the compiler cannot reorder
+                // them itself, loads and stores go to the same buffer)
 #pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    float4 s = rows[k][v];
-                    if (al >= 0) s = *reinterpret_cast<const float4 *>(wbuf + al * C + v * 128 + lane * 4);
-                    acc[v].x = fmaf(coef, s.x, acc[v].x);
-                    acc[v].y = fmaf(coef, s.y, acc[v].y);
-                    acc[v].z = fmaf(coef, s.z, acc[v].z);
-                    acc[v].w = fmaf(coef, s.w, acc[v].w);
+                for (int k0 = 0; k0 < K; k0 += 4) {
+                    float4 cur[4][NV];
+                    float gain[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        gain[i] = __shfl_sync(RN_FULL, coef_l, k0 + i);
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) cur[i][v] = *reinterpret_cast<const float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (!(rows & (1u << (k0 + i)))) continue;  // not loaded: the buffer holds stale rows there
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) {
+                            float4 s = cur[i][v];
+                            s.x = fmaf(gain[i], xv[v].x - s.x, s.x);
+                            s.y = fmaf(gain[i], xv[v].y - s.y, s.y);
+                            s.z = fmaf(gain[i], xv[v].z - s.z, s.z);
+                            s.w = fmaf(gain[i], xv[v].w - s.w, s.w);
+                            *reinterpret_cast<float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4) = s;
+                        }
+                    }
+                }
+                rn_fence_proxy_async();  // the updated rows are read by the bulk copy engine next
+                __syncwarp();
+                if (live_w) rn_bulk_s2g(slot + int64_t(a_l) * C, wbuf + lane * C, ROW_BYTES);
+                rn_bulk_commit();
+
+                // reads come after the writes of this step
+                if (p.mass_aware) {
+                    const float rm = (lane < K && r_l != 0.f) ? r_l * mass[ar_l] : 0.f;
+                    const float sr = rn_warp_sum(lane < K ? r_l : 0.f), srm = rn_warp_sum(rm);
+                    scale = sr / (srm + p.eps);
+                    r_l = rm;
+                }
+                // read rows that this step also wrote: from the updated copies in the buffer (rare: ~6 % of the pairs)
+                const bool live_r = lane < K && r_l != 0.f;
+                if (__any_sync(RN_FULL, live_r && alias_l >= 0)) {
+#pragma unroll 1
+                    for (int k = 0; k < K; ++k) {
+                        const float coef = __shfl_sync(RN_FULL, r_l, k);
+                        const int al = __shfl_sync(RN_FULL, alias_l, k);
+                        if (coef != 0.f && al >= 0) {
+#pragma unroll
+                            for (int v = 0; v < NV; ++v) {
+                                const float4 s = *reinterpret_cast<const float4 *>(wbuf + al * C + v * 128 + lane * 4);
+                                acc[v].x = fmaf(coef, s.x, acc[v].x);
+                                acc[v].y = fmaf(coef, s.y, acc[v].y);
+                                acc[v].z = fmaf(coef, s.z, acc[v].z);
+                                acc[v].w = fmaf(coef, s.w, acc[v].w);
+                            }
+                        }
+                    }
+                }
+                // the other read rows come by bulk copies too (a 512-byte bulk copy moves random rows at about twice
+                // the rate of per-lane loads), into the same buffer, once the outgoing copies have read it
+                rn_bulk_wait_read();
+                __syncwarp();
+                want = live_r && alias_l < 0;
+                row = ar_l;
+                coef_l = r_l;
+            } else {
+#pragma unroll
+                for (int k0 = 0; k0 < K; k0 += 4) {
+                    float4 cur[4][NV];
+                    float coef[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        coef[i] = __shfl_sync(RN_FULL, coef_l, k0 + i);
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) cur[i][v] = *reinterpret_cast<const float4 *>(wbuf + (k0 + i) * C + v * 128 + lane * 4);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (!(rows & (1u << (k0 + i)))) continue;  // not fetched: the buffer holds other rows there
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) {
+                            acc[v].x = fmaf(coef[i], cur[i][v].x, acc[v].x);
+                            acc[v].y = fmaf(coef[i], cur[i][v].y, acc[v].y);
+                            acc[v].z = fmaf(coef[i], cur[i][v].z, acc[v].z);
+                            acc[v].w = fmaf(coef[i], cur[i][v].w, acc[v].w);
+                        }
+                    }
                 }
             }
         }
@@ -655,9 +688,9 @@ __device__ __forceinline__ void rn_decode_pair_task(const RnDecodeParams &p, con
         }
 #pragma unroll
         for (int v = 0; v < NV; ++v) rn_store4<T>(y + v * 128 + lane * 4, acc[v]);
-        rn_bulk_wait_read();  // the buffer is free again once the outgoing copies have read it
-        __syncwarp();
+        __syncwarp();  // every lane is done with the buffer before the next pair's copies are requested
     }
+    return phase;
 }
 
 // 0 = launched, -1 = not this kernel's shape
@@ -667,20 +700,20 @@ static int rn_launch_decode_pair(const RnDecodeParams &p, int device, cudaStream
         return -1;
     } else {
         if (!(p.U == 2 && p.P == 64 && p.K[0] == 16 && p.K[1] == 16)) return -1;
-        const int wpc = RN_DECP_THREADS / 32;
+        if (p.C != 128 && p.C != 256) return -1;
+        const int threads = p.C == 128 ? RnDecPair<1>::THREADS : RnDecPair<2>::THREADS;
+        const int wpc = threads / 32;
         const int want = (p.B * p.H + wpc - 1) / wpc;
         const int cap = 2 * rn_sm_count(device);  // two resident CTAs per SM; the warps stride over the pairs
         const int grid = want < cap ? want : cap;
         if (p.C == 128) {
-            constexpr int smem = (RN_DECP_THREADS / 32) * 16 * 128 * 4;
+            constexpr int smem = (RnDecPair<1>::THREADS / 32) * 16 * 128 * 4;
             if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
-            rn_decode_pair_kernel<T, 1><<<grid, RN_DECP_THREADS, smem, stream>>>(p);
-        } else if (p.C == 256) {
-            constexpr int smem = (RN_DECP_THREADS / 32) * 16 * 256 * 4;
-            if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
-            rn_decode_pair_kernel<T, 2><<<grid, RN_DECP_THREADS, smem, stream>>>(p);
+            rn_decode_pair_kernel<T, 1><<<grid, threads, smem, stream>>>(p);
         } else {
-            return -1;
+            constexpr int smem = (RnDecPair<2>::THREADS / 32) * 16 * 256 * 4;
+            if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+            rn_decode_pair_kernel<T, 2><<<grid, threads, smem, stream>>>(p);
         }
         return 0;
     }
