@@ -70,6 +70,7 @@ int dispatch_fast(const FastParams &p, int U, int P, int K, cudaStream_t stream)
     if (U == 3 && P == 32 && K == 8) return launch_fast<T, 3, 32, 8>(p, stream);
     if (U == 2 && P == 16 && K == 4) return launch_fast<T, 2, 16, 4>(p, stream);
     if (U == 5 && P == 8 && K == 8) return launch_fast<T, 5, 8, 8>(p, stream);  // 32768 slots at the reference's radix limit
+    if (U == 4 && P == 8 && K == 16) return launch_fast<T, 4, 8, 16>(p, stream);  // 4096 slots, K above the radix
     return -1;
 }
 
@@ -275,7 +276,7 @@ int rn_addr_fwd_fast(const void *w_addr, const void *r_addr, int dtype, const in
                      double w_re_norm, double r_re_norm, int w_neg, int r_neg, int encode_batch, cudaStream_t stream) {
     if (r_addr != nullptr && Kw != Kr) return -1;
     const bool shape_ok = (U == 2 && P == 64 && Kw == 16) || (U == 3 && P == 32 && Kw == 8) || (U == 2 && P == 16 && Kw == 4) ||
-                          (U == 5 && P == 8 && Kw == 8);
+                          (U == 5 && P == 8 && Kw == 8) || (U == 4 && P == 8 && Kw == 16);
     if (!shape_ok) return -1;
     const size_t esz = dtype == RN_F32 ? 4 : 2;
     // the U*P block of a row must be contiguous and 16-byte aligned; the K outputs of a row too

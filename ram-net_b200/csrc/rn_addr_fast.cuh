@@ -243,10 +243,13 @@ __device__ __forceinline__ void rn_make_keys(const T *src, Key32 *dk) {
 template <typename T, int U, int P, int K>
 __device__ __forceinline__ void thread_decode(const T *src, const float rho, int (&content)[K], float (&weight)[K]) {
     using DKey = typename std::conditional<Raw<T>::wide, Key64, Key32>::type;
-    constexpr int NB = P / K;                 // digit blocks of K logits
+    // A digit contributes its KD = min(K, P) best logits.  With K > P the beam and the digit list are padded to K
+    // entries of score -inf: a padded candidate sorts with the masked ones and, like them, ends as a no-op entry.
+    constexpr int KD = K < P ? K : P;
+    constexpr int NB = P / KD;                // digit blocks of KD logits
     constexpr float LOG2E = 1.4426950408889634f;
     constexpr float LN2 = 0.6931471805599453f;
-    static_assert(P % K == 0 && (K & (K - 1)) == 0 && K >= 2, "P must be a multiple of the power-of-two K");
+    static_assert(P % KD == 0 && (K & (K - 1)) == 0 && (KD & (KD - 1)) == 0 && K >= 2, "K and min(K, P) powers of two, P a multiple of min(K, P)");
 
     float beam_s[K];
     int beam_i[K];
@@ -270,15 +273,15 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
             lse_total += xmax + fast_lg2(s) * LN2;
         }
         rn_make_keys<T, P>(src + u * P, dk);
-        static_for<0, NB>([&](auto BI) __attribute__((always_inline)) { oem_sort_desc<K>(dk + decltype(BI)::value * K); });
-        static_for<1, NB>([&](auto BI) __attribute__((always_inline)) { fold_topk<K>(dk, dk + decltype(BI)::value * K); });
-        // dk[0..K) = this digit's K best logits, sorted descending
+        static_for<0, NB>([&](auto BI) __attribute__((always_inline)) { oem_sort_desc<KD>(dk + decltype(BI)::value * KD); });
+        static_for<1, NB>([&](auto BI) __attribute__((always_inline)) { fold_topk<KD>(dk, dk + decltype(BI)::value * KD); });
+        // dk[0..KD) = this digit's KD best logits, sorted descending
 
         if (u == 0) {
 #pragma unroll
             for (int e = 0; e < K; ++e) {
-                beam_s[e] = digit_value<T>(dk[e]) + 0.0f;
-                beam_i[e] = digit_index(dk[e]);
+                beam_s[e] = e < KD ? digit_value<T>(dk[e < KD ? e : 0]) + 0.0f : -INFINITY;
+                beam_i[e] = e < KD ? digit_index(dk[e < KD ? e : 0]) : 0;
             }
         } else {
             // ---- candidates (i, j), (i+1)(j+1) <= K --------------------------------------------
@@ -286,8 +289,8 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
             int dp[K];
 #pragma unroll
             for (int e = 0; e < K; ++e) {
-                dv[e] = digit_value<T>(dk[e]);
-                dp[e] = digit_index(dk[e]) * stride;
+                dv[e] = e < KD ? digit_value<T>(dk[e < KD ? e : 0]) : -INFINITY;
+                dp[e] = e < KD ? digit_index(dk[e < KD ? e : 0]) * stride : 0;
             }
             // block 0: row i = 0 (sorted);  block 1: column j = 0, i >= 1 (sorted) + one pad
             Key64 best[K], blk[K];

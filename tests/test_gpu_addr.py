@@ -25,6 +25,9 @@ SHAPES = [
     (1, 1, 2, 100, 4, 64, 0, torch.bfloat16, 2.0),
     (2, 4, 5, 8, 40, 8, 2, torch.bfloat16, 1.5),     # 32768 slots at radix 8: thread-per-row kernel
     (1, 2, 5, 8, 20, 8, 1, torch.float32, 1.0),
+    (2, 4, 4, 8, 40, 16, 2, torch.bfloat16, 1.5),    # K above the radix: 8 logits per digit, beam of 16
+    (1, 2, 4, 8, 20, 16, 1, torch.float32, 1.0),
+    (1, 2, 4, 8, 20, 16, 1, torch.float16, 3.0),
 ]
 
 
@@ -148,7 +151,8 @@ def test_errors_are_runtime_errors():
 
 
 @pytest.mark.parametrize("U,P,K,dtype", [(2, 64, 16, torch.bfloat16), (3, 32, 8, torch.bfloat16), (2, 16, 4, torch.float32),
-                                         (2, 64, 16, torch.float16), (3, 32, 8, torch.float32), (2, 64, 16, torch.float32)])
+                                         (2, 64, 16, torch.float16), (3, 32, 8, torch.float32), (2, 64, 16, torch.float32),
+                                         (5, 8, 8, torch.bfloat16), (4, 8, 16, torch.bfloat16), (4, 8, 16, torch.float32)])
 def test_specialised_and_general_kernels_agree(U, P, K, dtype):
     """The thread-per-row kernel (contiguous U*P blocks) and the warp-cooperative kernel (any
     strides) implement the same total order: identical indices, weights equal to rounding.
