@@ -77,7 +77,7 @@ int dispatch_fast(const FastParams &p, int U, int P, int K, cudaStream_t stream)
 
 // ------------------------------------------------------------------------------------------
 // address backward, specialised: P/8 lanes per row (each lane owns 8 consecutive logits of every digit:
-// one 16-byte load / store per digit for 16-bit types), 2 Top-K entries per lane.  The K entries
+// one 16-byte load / store per digit for 16-bit types), K / (P/8) Top-K entries per lane.  The K entries
 // are scattered into a per-row accumulator in shared memory (U*P floats) by digit, then every lane
 // reads back its own 8 positions per digit:
 //   d logit[u][p] = sum_{k : digit_u(content_k) = p} D'_k  -  softmax_u[p] * (1 - rho) * sum_k D_k
@@ -152,8 +152,10 @@ template <typename T, int U, int P, int K>
 __global__ void __launch_bounds__(FAST_THREADS) rn_addr_bwd_fast_kernel(const FastBwdParams p) {
     constexpr int LPR = P / 8;              // lanes per row
     constexpr int RPC = FAST_THREADS / LPR; // rows per CTA
-    static_assert(K == 2 * LPR, "two Top-K entries per lane");
-    __shared__ __align__(16) float accum[RPC][U * P];
+    constexpr int EPL = K / LPR;            // Top-K entries per lane
+    constexpr int ROW = U * P + (LPR <= 2 ? 4 : 0);  // accumulator stride: short rows are staggered over the banks
+    static_assert(K % LPR == 0 && EPL % 2 == 0, "an even number of Top-K entries per lane");
+    __shared__ __align__(16) float accum[RPC][ROW];
 
     const int tid = threadIdx.x, lr = tid % LPR, rc = tid / LPR;
     const int64_t item = int64_t(blockIdx.x) * RPC + rc;  // rows of one tensor are adjacent: item = which * n_rows + row
@@ -169,26 +171,35 @@ __global__ void __launch_bounds__(FAST_THREADS) rn_addr_bwd_fast_kernel(const Fa
     // the lanes of a row are LPR consecutive lanes of one warp
     const unsigned gmask = (LPR >= 32 ? 0xffffffffu : ((1u << LPR) - 1u)) << ((tid & 31) & ~(LPR - 1));
 
-    // ---- this lane's two entries -----------------------------------------------------------------
-    const int64_t o = b * p.ob + h * p.oh + t * p.ot + (which ? K : 0) + 2 * lr;
-    const int64_t g = b * p.gb + h * p.gh + t * p.gt + (which ? K : 0) + 2 * lr;
-    const int2 ix = *reinterpret_cast<const int2 *>(p.idx + o);
-    const float2 wv = *reinterpret_cast<const float2 *>(p.val + o);
-    const float2 dv = *reinterpret_cast<const float2 *>(p.d_val + g);
-    const float w0 = p.sign[which] * wv.x, w1 = p.sign[which] * wv.y;
-    float d0 = dv.x * w0, d1 = dv.y * w1;
-    int c0 = ix.x % p.A + shift, c1 = ix.y % p.A + shift;
-    c0 = c0 >= p.A ? c0 - p.A : c0;
-    c1 = c1 >= p.A ? c1 - p.A : c1;
-    float dsum = d0 + d1, wsum = w0 + w1;
+    // ---- this lane's entries -----------------------------------------------------------------------
+    const int64_t o = b * p.ob + h * p.oh + t * p.ot + (which ? K : 0) + EPL * lr;
+    const int64_t g = b * p.gb + h * p.gh + t * p.gt + (which ? K : 0) + EPL * lr;
+    int ce[EPL];
+    float we[EPL], de[EPL];
+    float dsum = 0.f, wsum = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; e += 2) {
+        const int2 ix = *reinterpret_cast<const int2 *>(p.idx + o + e);
+        const float2 wv = *reinterpret_cast<const float2 *>(p.val + o + e);
+        const float2 dv = *reinterpret_cast<const float2 *>(p.d_val + g + e);
+        we[e] = p.sign[which] * wv.x;
+        we[e + 1] = p.sign[which] * wv.y;
+        de[e] = dv.x * we[e];
+        de[e + 1] = dv.y * we[e + 1];
+        int c0 = ix.x % p.A + shift, c1 = ix.y % p.A + shift;
+        ce[e] = c0 >= p.A ? c0 - p.A : c0;
+        ce[e + 1] = c1 >= p.A ? c1 - p.A : c1;
+        dsum += de[e] + de[e + 1];
+        wsum += we[e] + we[e + 1];
+    }
 #pragma unroll
     for (int off = 1; off < LPR; off <<= 1) {
         dsum += __shfl_xor_sync(gmask, dsum, off);
         wsum += __shfl_xor_sync(gmask, wsum, off);
     }
     if (rho != 0.f && wsum > 0.f) {
-        d0 -= rho * (w0 / wsum) * dsum;
-        d1 -= rho * (w1 / wsum) * dsum;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) de[e] -= rho * (we[e] / wsum) * dsum;
     }
     const float tail = (1.f - rho) * dsum;
 
@@ -226,14 +237,13 @@ __global__ void __launch_bounds__(FAST_THREADS) rn_addr_bwd_fast_kernel(const Fa
         *reinterpret_cast<float4 *>(acc + u * P + lr * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __syncwarp(gmask);
-    {
-        int a0 = c0, a1 = c1;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+        int a = ce[e];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            atomicAdd(acc + u * P + a0 % P, d0);
-            atomicAdd(acc + u * P + a1 % P, d1);
-            a0 /= P;
-            a1 /= P;
+            atomicAdd(acc + u * P + a % P, de[e]);
+            a /= P;
         }
     }
     __syncwarp(gmask);
@@ -264,6 +274,8 @@ int dispatch_bwd_fast(const FastBwdParams &p, int U, int P, int K, cudaStream_t 
     if (U == 2 && P == 64 && K == 16) return launch_bwd_fast<T, 2, 64, 16>(p, stream);
     if (U == 3 && P == 32 && K == 8) return launch_bwd_fast<T, 3, 32, 8>(p, stream);
     if (U == 2 && P == 16 && K == 4) return launch_bwd_fast<T, 2, 16, 4>(p, stream);
+    if (U == 5 && P == 8 && K == 8) return launch_bwd_fast<T, 5, 8, 8>(p, stream);
+    if (U == 4 && P == 8 && K == 16) return launch_bwd_fast<T, 4, 8, 16>(p, stream);
     return -1;
 }
 
@@ -312,7 +324,8 @@ int rn_addr_bwd_fast(const int32_t *idx, const float *val, const int64_t *out_st
                      int64_t A, int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm, int w_neg, int r_neg,
                      cudaStream_t stream) {
     if (r_addr != nullptr && Kw != Kr) return -1;
-    const bool shape_ok = (U == 2 && P == 64 && Kw == 16) || (U == 3 && P == 32 && Kw == 8) || (U == 2 && P == 16 && Kw == 4);
+    const bool shape_ok = (U == 2 && P == 64 && Kw == 16) || (U == 3 && P == 32 && Kw == 8) || (U == 2 && P == 16 && Kw == 4) ||
+                          (U == 5 && P == 8 && Kw == 8) || (U == 4 && P == 8 && Kw == 16);
     if (!shape_ok) return -1;
     const size_t esz = dtype == RN_F32 ? 4 : 2;
     // logits and their gradients: the U*P block of a row contiguous, rows 16-byte aligned (32 for fp32 pairs of float4)

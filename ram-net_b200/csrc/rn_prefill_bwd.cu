@@ -11,15 +11,18 @@
 //            read:  d_slot[a] += r d_y;   write:  d_gain = <d_slot[a], delta>,
 //            d_x += gain d_slot[a],  d_slot[a] *= 1 - gain;
 //   scalar   (one CTA per (b,h), chunks and rounds backward):  the mass chain: d_w, d_gamma, d_mass.
-// Partial dot products of the channel slices are combined with float atomics (d_r, d_gain).
+// The workspaces of the sweeps are laid out per channel slice, so that a CTA streams through memory of its own:
+// delta as [bh][slice][t][k][channels of the slice] and the partial dot products of a slice (d_r from the replay,
+// d_gain from the reverse sweep) as [bh][slice][t][k]; a reduce kernel adds the slices (fixed order, no atomics).
 #include "rn_prefill.cuh"
 
 struct RnGsuBwdParams {
     RnGsuParams f;            // forward description (idx/val, x, gamma, mask, records, ...)
     const void *dy;           // (B,H,T,C) upstream gradient of y, dtype of x
     int64_t dyb, dyh, dyt;
-    float *delta;             // workspace [(bh*T + t)*Kw + k][C]
-    float *dgain;             // workspace [(bh*T + t)*Kw + k], zeroed by the caller
+    float *delta;             // workspace [(bh*nslices + slice)*T + t][Kw][cs]
+    float *part;              // workspace [(bh*nslices + slice)*T + t][Kw + Kr]: d_gain (k < Kw) and d_r partial sums
+    float *dgain;             // workspace [(bh*T + t)*Kw + k], written by the reduce kernel
     float *dval;              // output (B,H,Kw+Kr,T) via strides, zeroed by the caller
     int64_t vb, vh, vk, vt;
     void *dx;                 // output (B,H,T,C), dtype of x
@@ -47,9 +50,11 @@ __device__ __forceinline__ float rn_group_sum(float v, int G, unsigned mask) {
 // other events of a slot form a chain that one thread group walks with the row in registers, forwards
 // in time in the replay and against it in the reverse sweep.
 //   replay   write: delta = x - slot is stored for the reverse sweep, slot += gain * delta
-//            read:  d_r += <slot, d_y>   (float atomics across the channel slices)
+//            read:  this slice's part of d_r = <slot, d_y>
 //   reverse  read:  d_slot += r * d_y
-//            write: d_gain += <d_slot, delta>, d_x += gain * d_slot, d_slot *= 1 - gain
+//            write: this slice's part of d_gain = <d_slot, delta>, d_x += gain * d_slot, d_slot *= 1 - gain
+// Every (token, k) of a chunk gets its partial dot product from exactly one thread (zero for a no-op event), so the
+// partial sums need no clearing.
 // MODEL: the instance for Kw = Kr = 16 with 64-token chunks (see rn_gsu_apply_fast_kernel)
 template <typename T, int CS, int EV, bool REVERSE, bool MODEL = false>
 __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(const RnGsuBwdParams bp, const int tpt_log2_) {
@@ -147,9 +152,10 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
         const unsigned char *rec = rec0 + (it & 1) * rec_stride;
         const uint2 *e_pair = reinterpret_cast<const uint2 *>(rec);
         const uint16_t *heads = reinterpret_cast<const uint16_t *>(rec + size_t(NEp) * 8);
-        // per-write-event rows in the workspaces: index of (t, k) = (bh*T + t)*Kw + k
-        const int64_t wchunk = (int64_t(bh) * p.T + t0) * Kw;
-        const int64_t wbase = wchunk + int64_t(tok) * Kw;
+        // this slice's rows of the workspaces: write event (t, k) at (t*Kw + k)*CS in delta, event (t, k) at t*KT + k in part
+        float *dchunk = bp.delta + ((int64_t(bh) * p.nslices + slice) * p.T + t0) * Kw * CS;
+        float *dtok = dchunk + int64_t(tok) * Kw * CS + sub * 4;
+        float *pchunk = bp.part + ((int64_t(bh) * p.nslices + slice) * p.T + t0) * KT;
 
         if (q == 0 && tok < L) {
             if (!REVERSE) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
@@ -177,9 +183,11 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                 dl[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (kind < RN_KIND_HEAD) {
                     row[i] = *reinterpret_cast<const float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4);
-                    if (REVERSE && wr_of(jb + i) && chan_ok) dl[i] = *reinterpret_cast<const float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4);
-                } else if (REVERSE && kind <= RN_KIND_LATER && wr_of(jb + i)) {
-                    late |= 1u << (jb + i);
+                    if (REVERSE && wr_of(jb + i) && chan_ok) dl[i] = *reinterpret_cast<const float4 *>(dtok + k * CS);
+                } else if (kind <= RN_KIND_LATER) {
+                    if (REVERSE && wr_of(jb + i)) late |= 1u << (jb + i);
+                } else if (tok_ok && (MODEL || k < KT) && sub == 0 && wr_of(jb + i) == REVERSE) {
+                    pchunk[tok * KT + k] = 0.f;  // a no-op event
                 }
             }
 #pragma unroll
@@ -192,7 +200,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                 if (!REVERSE) {
                     if (wr_of(jb + i)) {
                         const float4 d = make_float4(xv.x - s.x, xv.y - s.y, xv.z - s.z, xv.w - s.w);
-                        if (chan_ok) *reinterpret_cast<float4 *>(bp.delta + (wbase + k) * C + c0 + sub * 4) = d;
+                        if (chan_ok) *reinterpret_cast<float4 *>(dtok + k * CS) = d;
                         s.x = fmaf(cf, d.x, s.x);
                         s.y = fmaf(cf, d.y, s.y);
                         s.z = fmaf(cf, d.z, s.z);
@@ -201,7 +209,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                     } else {
                         float dot = s.x * dyv.x + s.y * dyv.y + s.z * dyv.z + s.w * dyv.w;
                         dot = rn_group_sum(dot, G, gmask);
-                        if (sub == 0) atomicAdd(bp.dval + b * bp.vb + h * bp.vh + int64_t(k) * bp.vk + int64_t(t0 + tok) * bp.vt, dot);
+                        if (sub == 0) pchunk[tok * KT + k] = dot;
                     }
                 } else {
                     if (!wr_of(jb + i)) {
@@ -212,7 +220,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                     } else {
                         float dot = s.x * dl[i].x + s.y * dl[i].y + s.z * dl[i].z + s.w * dl[i].w;
                         dot = rn_group_sum(dot, G, gmask);
-                        if (sub == 0) atomicAdd(bp.dgain + wbase + k, dot);
+                        if (sub == 0) pchunk[tok * KT + k] = dot;
                         acc.x = fmaf(cf, s.x, acc.x);
                         acc.y = fmaf(cf, s.y, acc.y);
                         acc.z = fmaf(cf, s.z, acc.z);
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                 float4 s = *reinterpret_cast<float4 *>(row);
                 int ct = int(__umulhi(uint32_t(e), kt_magic)), ck = e - ct * KT;
                 float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (REVERSE && ck < Kw && cok) dl = *reinterpret_cast<const float4 *>(bp.delta + (wchunk + int64_t(ct) * Kw + ck) * C + c0 + csub * 4);
+                if (REVERSE && ck < Kw && cok) dl = *reinterpret_cast<const float4 *>(dchunk + (ct * Kw + ck) * CS + csub * 4);
                 for (int guard = 0; guard < RN_GSU_NE_MAX; ++guard) {
                     // the following event's record (and delta) is requested before this one is applied
                     const bool more_ev = (pr.y & RN_LINK_NEXT) != 0;
@@ -251,7 +259,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                         ct_n = int(__umulhi(uint32_t(en), kt_magic));
                         ck_n = en - ct_n * KT;
                         if (REVERSE && ck_n < Kw && cok)
-                            dl_n = *reinterpret_cast<const float4 *>(bp.delta + (wchunk + int64_t(ct_n) * Kw + ck_n) * C + c0 + csub * 4);
+                            dl_n = *reinterpret_cast<const float4 *>(dchunk + (ct_n * Kw + ck_n) * CS + csub * 4);
                     }
                     const float cf = __uint_as_float(pr.x);
                     const bool wr = ck < Kw;
@@ -259,7 +267,7 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                         if (wr) {
                             const float4 xr = *reinterpret_cast<const float4 *>(xt + ct * CS + csub * 4);
                             const float4 d = make_float4(xr.x - s.x, xr.y - s.y, xr.z - s.z, xr.w - s.w);
-                            if (cok) *reinterpret_cast<float4 *>(bp.delta + (wchunk + int64_t(ct) * Kw + ck) * C + c0 + csub * 4) = d;
+                            if (cok) *reinterpret_cast<float4 *>(dchunk + (ct * Kw + ck) * CS + csub * 4) = d;
                             s.x = fmaf(cf, d.x, s.x);
                             s.y = fmaf(cf, d.y, s.y);
                             s.z = fmaf(cf, d.z, s.z);
@@ -269,13 +277,13 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                         const float4 dyr = *reinterpret_cast<const float4 *>(dyt + ct * CS + csub * 4);
                         float dot = wr ? 0.f : s.x * dyr.x + s.y * dyr.y + s.z * dyr.z + s.w * dyr.w;
                         dot = rn_group_sum(dot, G, gmask);
-                        if (!wr && csub == 0) atomicAdd(bp.dval + b * bp.vb + h * bp.vh + int64_t(ck) * bp.vk + int64_t(t0 + ct) * bp.vt, dot);
+                        if (!wr && csub == 0) pchunk[ct * KT + ck] = dot;
                     } else {
                         const float4 dyr = *reinterpret_cast<const float4 *>(dyt + ct * CS + csub * 4);
                         float dot = wr ? s.x * dl.x + s.y * dl.y + s.z * dl.z + s.w * dl.w : 0.f;
                         dot = rn_group_sum(dot, G, gmask);
                         if (wr) {
-                            if (csub == 0) atomicAdd(bp.dgain + wchunk + int64_t(ct) * Kw + ck, dot);
+                            if (csub == 0) pchunk[ct * KT + ck] = dot;
                             *reinterpret_cast<float4 *>(dxlate + (ct * Kw + ck) * CS + csub * 4) = make_float4(cf * s.x, cf * s.y, cf * s.z, cf * s.w);
                             const float keep = 1.f - cf;
                             s.x *= keep; s.y *= keep; s.z *= keep; s.w *= keep;
@@ -330,6 +338,37 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
             if (sg * 4 < cvalid)
                 *reinterpret_cast<float4 *>(dst + int64_t(a) * C + sg * 4) = *reinterpret_cast<const float4 *>(S + rn_row_of_slot(uint32_t(a), A, p.row_shift) * CS + sg * 4);
         }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// reduce kernel: adds the channel slices' partial dot products, slice 0 first
+// ------------------------------------------------------------------------------------------
+// One CTA per (b,h) and 32 tokens.  d_gain of the writes goes to the compact table the scalar kernel reads, d_r of
+// the reads to the caller's gradient tensor, through a shared-memory transpose because that tensor runs along time.
+constexpr int RN_RED_TOKENS = 32;
+constexpr int RN_RED_THREADS = 256;
+__global__ void __launch_bounds__(RN_RED_THREADS) rn_gsu_bwd_reduce_kernel(const RnGsuBwdParams bp) {
+    const RnGsuParams &p = bp.f;
+    extern __shared__ float red_tile[];  // [Kr][RN_RED_TOKENS + 1]
+    const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+    const int t0 = blockIdx.x * RN_RED_TOKENS;
+    const int nt = min(RN_RED_TOKENS, p.T - t0);
+    const int Kw = p.Kw, Kr = p.Kr, KT = Kw + Kr;
+    const int64_t slice_stride = int64_t(p.T) * KT;
+    const float *src = bp.part + (int64_t(bh) * p.nslices * p.T + t0) * KT;
+    for (int i = threadIdx.x; i < nt * KT; i += RN_RED_THREADS) {
+        float sum = 0.f;
+        for (int sl = 0; sl < p.nslices; ++sl) sum += src[sl * slice_stride + i];
+        const int t = i / KT, k = i - t * KT;
+        if (k < Kw) bp.dgain[(int64_t(bh) * p.T + t0 + t) * Kw + k] = sum;
+        else red_tile[(k - Kw) * (RN_RED_TOKENS + 1) + t] = sum;
+    }
+    __syncthreads();
+    float *dst = bp.dval + b * bp.vb + h * bp.vh + int64_t(t0) * bp.vt;
+    for (int i = threadIdx.x; i < Kr * RN_RED_TOKENS; i += RN_RED_THREADS) {
+        const int k = i / RN_RED_TOKENS, t = i - k * RN_RED_TOKENS;
+        if (t < nt) dst[int64_t(Kw + k) * bp.vk + int64_t(t) * bp.vt] = red_tile[k * (RN_RED_TOKENS + 1) + t];
     }
 }
 
@@ -492,7 +531,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
 // host side
 // ------------------------------------------------------------------------------------------
 struct RnBwdLayout {
-    size_t off_fwd, off_prev_mass, off_read_mass, off_dgain, off_delta, total;
+    size_t off_fwd, off_prev_mass, off_read_mass, off_dgain, off_part, off_delta, total;
 };
 
 static void rn_bwd_layout(const RnGsuPlan &pl, int64_t B, int64_t H, int64_t T, int64_t C, int64_t Kw, int64_t Kr,
@@ -506,8 +545,10 @@ static void rn_bwd_layout(const RnGsuPlan &pl, int64_t B, int64_t H, int64_t T, 
     off = rn_align(off + size_t(B * H * T * Kr) * 4, 256);
     lo->off_dgain = off;
     off = rn_align(off + size_t(B * H * T * Kw) * 4, 256);
+    lo->off_part = off;
+    off = rn_align(off + size_t(B * H * T * (Kw + Kr)) * size_t(pl.nslices) * 4, 256);
     lo->off_delta = off;
-    off = rn_align(off + size_t(B * H * T * Kw) * size_t(C) * 4, 256);
+    off = rn_align(off + size_t(B * H * T * Kw) * size_t(pl.nslices) * size_t(pl.cs) * 4, 256);
     lo->total = off;
 }
 
@@ -581,6 +622,11 @@ static int rn_run_bwd(const RnGsuBwdParams &bp, const RnGsuPlan &pl, int dtype, 
     if (int rc = rn_launch_sweep<T, true>(bp, pl, stream)) return rc;
     RN_CUDA(cudaGetLastError());
     rn_prof_mark(stream);
+    {
+        const dim3 grid(unsigned((bp.f.T + RN_RED_TOKENS - 1) / RN_RED_TOKENS), unsigned(bp.f.B * bp.f.H));
+        rn_gsu_bwd_reduce_kernel<<<grid, RN_RED_THREADS, size_t(bp.f.Kr) * (RN_RED_TOKENS + 1) * 4, stream>>>(bp);
+        RN_CUDA(cudaGetLastError());
+    }
     const size_t ev_smem = size_t(pl.L) * (bp.f.Kw + 3 * bp.f.Kr) * 4;
     const bool smem_table = size_t(bp.f.A) * 4 + ev_smem <= 200 * 1024;
     const size_t smem = (smem_table ? size_t(bp.f.A) * 4 : 0) + ev_smem;
@@ -663,6 +709,7 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     bp.dy = d_y; bp.dyb = dy_strides[0]; bp.dyh = dy_strides[1]; bp.dyt = dy_strides[2];
     bp.delta = reinterpret_cast<float *>(ws + lo.off_delta);
     bp.dgain = reinterpret_cast<float *>(ws + lo.off_dgain);
+    bp.part = reinterpret_cast<float *>(ws + lo.off_part);
     bp.dval = d_val; bp.vb = dval_strides[0]; bp.vh = dval_strides[1]; bp.vk = dval_strides[2]; bp.vt = dval_strides[3];
     bp.dx = d_x; bp.dxb = dx_strides[0]; bp.dxh = dx_strides[1]; bp.dxt = dx_strides[2];
     bp.dgamma = d_gamma;
@@ -670,7 +717,6 @@ extern "C" int rn_gsu_bwd(const int32_t *idx, const float *val, const int64_t *i
     bp.dmass_post = d_mass_post; bp.dmass_out = d_mass; bp.dmass_ws = d_mass;
 
     RN_REQUIRE(pl.smem_tables, "the backward pass needs the per-head mass table to fit shared memory (A=%lld)", (long long)A);
-    RN_CUDA(cudaMemsetAsync(bp.dgain, 0, size_t(B * H * T * Kw) * 4, stream));
 
     if (dtype == RN_F32) return rn_run_bwd<float>(bp, pl, dtype, stream);
     if (dtype == RN_F16) return rn_run_bwd<__half>(bp, pl, dtype, stream);
