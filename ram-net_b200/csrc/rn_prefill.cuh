@@ -189,6 +189,10 @@ __device__ __forceinline__ bool rn_mbar_wait_bounded(uint64_t *bar, uint32_t par
     }
     return true;
 }
+// asks the L2 for a contiguous piece of global memory (16-byte aligned, a multiple of 16 bytes) ahead of its use
+__device__ __forceinline__ void rn_bulk_prefetch_l2(const void *gptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
 // shared -> global bulk copy (one bulk group per commit); wait_read returns once the copies of this thread's
 // groups have read their shared-memory source
 __device__ __forceinline__ void rn_bulk_s2g(void *dst, const void *src, uint32_t bytes) {

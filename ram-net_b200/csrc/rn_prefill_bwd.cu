@@ -156,6 +156,12 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
         float *dchunk = bp.delta + ((int64_t(bh) * p.nslices + slice) * p.T + t0) * Kw * CS;
         float *dtok = dchunk + int64_t(tok) * Kw * CS + sub * 4;
         float *pchunk = bp.part + ((int64_t(bh) * p.nslices + slice) * p.T + t0) * KT;
+        if (REVERSE && more && tid == 32) {
+            // the deltas of the chunk after this one: one contiguous piece of this slice's workspace
+            const int tn = (chunk + step) * L;
+            rn_bulk_prefetch_l2(bp.delta + ((int64_t(bh) * p.nslices + slice) * p.T + tn) * Kw * CS,
+                                uint32_t(min(L, p.T - tn) * Kw * CS * 4));
+        }
 
         if (q == 0 && tok < L) {
             if (!REVERSE) *reinterpret_cast<float4 *>(xt + tok * CS + sub * 4) = xv;
@@ -359,6 +365,7 @@ __global__ void __launch_bounds__(RN_RED_THREADS) rn_gsu_bwd_reduce_kernel(const
     const float *src = bp.part + (int64_t(bh) * p.nslices * p.T + t0) * KT;
     for (int i = threadIdx.x; i < nt * KT; i += RN_RED_THREADS) {
         float sum = 0.f;
+#pragma unroll 8
         for (int sl = 0; sl < p.nslices; ++sl) sum += src[sl * slice_stride + i];
         const int t = i / KT, k = i - t * KT;
         if (k < Kw) bp.dgain[(int64_t(bh) * p.T + t0 + t) * Kw + k] = sum;
@@ -395,7 +402,7 @@ __device__ __forceinline__ RnGateBwd rn_gate_bwd(float d_gain, float d_mass, flo
 }
 
 template <typename T, bool SMEM_TABLE, int EPT, bool MASS_AWARE>
-__global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const RnGsuBwdParams bp) {
+__global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_scalar_bwd_kernel(const RnGsuBwdParams bp) {
     const RnGsuParams &p = bp.f;
     extern __shared__ __align__(16) unsigned char dyn[];
     __shared__ float gam[RN_GSU_LMAX];
@@ -403,7 +410,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
 
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh % p.H;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, NT = blockDim.x;  // the thread count and events per thread of the schedule kernel
     const int A = p.A, Kw = p.Kw, Kr = p.Kr, KT = p.Kw + p.Kr, NEp = p.NEp;
     const bool pow2 = (A & (A - 1)) == 0;
 
@@ -414,13 +421,13 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
     float *rd_r = rd_u + size_t(p.L) * Kr;
     float *rd_dot = rd_r + size_t(p.L) * Kr;
     const float *src = bp.dmass_post + int64_t(bh) * A;
-    for (int a = tid; a < A; a += RN_GSU_THREADS)
+    for (int a = tid; a < A; a += NT)
         if (SMEM_TABLE || src != dmass) dmass[a] = src[a];
 
     int ev_t[EPT], ev_k[EPT];
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
-        const int e = j * RN_GSU_THREADS + tid;
+        const int e = j * NT + tid;
         ev_t[j] = e / KT;
         ev_k[j] = e - ev_t[j] * KT;
     }
@@ -428,16 +435,59 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
     const int64_t ibase = b * p.ib + h * p.ih;
     __syncthreads();
 
+    // What a chunk needs from global memory is requested one chunk ahead, so that the loads are in flight during
+    // the rounds of the chunk before: per event its record word, address, weight, the mass it saw and d_gain
+    // (a write) or <slot, d_y> (a read of the mass-aware variant); per token gamma; the number of rounds.
+    struct Ev {
+        uint32_t meta;
+        int raw;
+        float w, m, g;
+    };
+    auto request = [&](const int chunk, Ev (&ev)[EPT], float &gam_r, int &rounds) {
+        const int t0 = chunk * p.L;
+        const int Lc = chunk >= 0 ? min(p.L, p.T - t0) : 0;
+        const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + max(chunk, 0)) * p.rec_bytes;
+        const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
+        rounds = chunk >= 0 ? int(*reinterpret_cast<const uint32_t *>(rec)) : 0;
+        gam_r = tid < Lc ? rn_to_float<T>(gamma[(t0 + tid) * p.gt]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            ev[j] = Ev{RN_EV_DEAD, 0, 0.f, 0.f, 0.f};
+            const int e = j * NT + tid;
+            const bool is_write = ev_k[j] < Kw;
+            if (ev_t[j] < Lc && e < NEp && (is_write || MASS_AWARE)) {
+                ev[j].meta = e_meta[ev_t[j] * KT + ev_k[j]];
+                const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
+                ev[j].raw = p.idx[o];
+                ev[j].w = p.val[o];
+                if (is_write) {
+                    const int64_t wi = (int64_t(bh) * p.T + t0 + ev_t[j]) * Kw + ev_k[j];
+                    ev[j].m = p.prev_mass[wi];
+                    ev[j].g = bp.dgain[wi];
+                } else {
+                    ev[j].m = p.read_mass[(int64_t(bh) * p.T + t0 + ev_t[j]) * Kr + (ev_k[j] - Kw)];
+                    ev[j].g = bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt];
+                }
+            }
+        }
+    };
+    Ev ev_next[EPT];
+    float gam_next;
+    int rounds_next;
+    request(p.nchunks - 1, ev_next, gam_next, rounds_next);
+
     for (int chunk = p.nchunks - 1; chunk >= 0; --chunk) {
         const int t0 = chunk * p.L;
         const int Lc = min(p.L, p.T - t0);
-        const unsigned char *rec = p.records + (int64_t(bh) * p.nchunks + chunk) * p.rec_bytes;
-        const uint32_t *e_meta = reinterpret_cast<const uint32_t *>(rec + RN_GSU_HDR_BYTES);
-        const int R = int(*reinterpret_cast<const uint32_t *>(rec));
-        if (tid < Lc) gam[tid] = rn_to_float<T>(gamma[(t0 + tid) * p.gt]);
-        for (int i = tid; i < Lc * Kw; i += RN_GSU_THREADS) dg_term[i] = 0.f;
+        const int R = rounds_next;
+        Ev cur[EPT];
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) cur[j] = ev_next[j];
+        if (tid < Lc) gam[tid] = gam_next;
+        request(chunk - 1, ev_next, gam_next, rounds_next);
+        for (int i = tid; i < Lc * Kw; i += NT) dg_term[i] = 0.f;
         if (MASS_AWARE)
-            for (int i = tid; i < Lc * Kr; i += RN_GSU_THREADS) rd_u[i] = rd_r[i] = rd_dot[i] = 0.f;
+            for (int i = tid; i < Lc * Kr; i += NT) rd_u[i] = rd_r[i] = rd_dot[i] = 0.f;
         __syncthreads();
 
         // this thread's live events: round, slot, weight, mass seen, d_gain (writes) / <slot, d_y> (reads)
@@ -449,28 +499,17 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
             er[j] = -1;
             ea[j] = 0;
             ew[j] = em[j] = eg[j] = 0.f;
-            const int e = j * RN_GSU_THREADS + tid;
-            const bool is_write = ev_k[j] < Kw;
-            if (ev_t[j] < Lc && e < NEp && (is_write || MASS_AWARE)) {
-                const uint32_t meta = e_meta[ev_t[j] * KT + ev_k[j]];
-                if (!(meta & RN_EV_DEAD)) {
-                    const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
-                    const int raw = p.idx[o];
-                    er[j] = rn_ev_round(meta);
-                    ea[j] = pow2 ? uint32_t(raw & (A - 1)) : uint32_t(raw % A);
-                    ew[j] = fabsf(p.val[o]);
-                    if (is_write) {
-                        const int64_t wi = (int64_t(bh) * p.T + t0 + ev_t[j]) * Kw + ev_k[j];
-                        em[j] = p.prev_mass[wi];
-                        eg[j] = bp.dgain[wi];
-                    } else {
-                        const int kr = ev_k[j] - Kw;
-                        em[j] = p.read_mass[(int64_t(bh) * p.T + t0 + ev_t[j]) * Kr + kr];
-                        eg[j] = bp.dval[b * bp.vb + h * bp.vh + int64_t(ev_k[j]) * bp.vk + int64_t(t0 + ev_t[j]) * bp.vt];
-                        rd_u[ev_t[j] * Kr + kr] = ew[j] * em[j];
-                        rd_r[ev_t[j] * Kr + kr] = ew[j];
-                        rd_dot[ev_t[j] * Kr + kr] = eg[j];
-                    }
+            if (!(cur[j].meta & RN_EV_DEAD)) {
+                er[j] = rn_ev_round(cur[j].meta);
+                ea[j] = pow2 ? uint32_t(cur[j].raw & (A - 1)) : uint32_t(cur[j].raw % A);
+                ew[j] = fabsf(cur[j].w);
+                em[j] = cur[j].m;
+                eg[j] = cur[j].g;
+                if (ev_k[j] >= Kw) {
+                    const int kr = ev_k[j] - Kw;
+                    rd_u[ev_t[j] * Kr + kr] = ew[j] * em[j];
+                    rd_r[ev_t[j] * Kr + kr] = ew[j];
+                    rd_dot[ev_t[j] * Kr + kr] = eg[j];
                 }
             }
         }
@@ -523,7 +562,7 @@ __global__ void __launch_bounds__(RN_GSU_THREADS) rn_gsu_scalar_bwd_kernel(const
     }
     if (SMEM_TABLE) {
         float *dst = bp.dmass_out + int64_t(bh) * A;
-        for (int a = tid; a < A; a += RN_GSU_THREADS) dst[a] = dmass[a];
+        for (int a = tid; a < A; a += NT) dst[a] = dmass[a];
     }
 }
 
@@ -597,15 +636,15 @@ template <typename T, bool SMEM, bool MA>
 static int rn_launch_scalar_bwd(const RnGsuBwdParams &bp, const RnGsuPlan &pl, size_t smem, cudaStream_t stream) {
     const int bh = bp.f.B * bp.f.H;
 #define RN_CASE(E)                                                                                                   \
-    if (pl.ept == E) {                                                                                               \
+    if (pl.sched_ept == E) {                                                                                         \
         RN_CUDA(cudaFuncSetAttribute(rn_gsu_scalar_bwd_kernel<T, SMEM, E, MA>,                                       \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));                       \
-        rn_gsu_scalar_bwd_kernel<T, SMEM, E, MA><<<bh, RN_GSU_THREADS, smem, stream>>>(bp);                          \
+        rn_gsu_scalar_bwd_kernel<T, SMEM, E, MA><<<bh, pl.sched_threads, smem, stream>>>(bp);                        \
         return 0;                                                                                                    \
     }
-    RN_CASE(1) RN_CASE(2) RN_CASE(4) RN_CASE(8) RN_CASE(16)
+    RN_CASE(2) RN_CASE(4)
 #undef RN_CASE
-    rn_set_error("no scalar backward kernel for %d events per thread", pl.ept);
+    rn_set_error("no scalar backward kernel for %d events per thread", pl.sched_ept);
     return 1;
 }
 
