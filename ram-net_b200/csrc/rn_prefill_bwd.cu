@@ -363,13 +363,29 @@ __global__ void __launch_bounds__(RN_RED_THREADS) rn_gsu_bwd_reduce_kernel(const
     const int Kw = p.Kw, Kr = p.Kr, KT = Kw + Kr;
     const int64_t slice_stride = int64_t(p.T) * KT;
     const float *src = bp.part + (int64_t(bh) * p.nslices * p.T + t0) * KT;
-    for (int i = threadIdx.x; i < nt * KT; i += RN_RED_THREADS) {
-        float sum = 0.f;
-#pragma unroll 8
-        for (int sl = 0; sl < p.nslices; ++sl) sum += src[sl * slice_stride + i];
+    auto put = [&](const int i, const float sum) {
         const int t = i / KT, k = i - t * KT;
         if (k < Kw) bp.dgain[(int64_t(bh) * p.T + t0 + t) * Kw + k] = sum;
         else red_tile[(k - Kw) * (RN_RED_TOKENS + 1) + t] = sum;
+    };
+    if (((slice_stride | (int64_t(t0) * KT) | (int64_t(nt) * KT)) & 3) == 0) {
+        // four entries per thread and slice: sixteen-byte loads, all slices of an entry requested before the sum
+        for (int i = threadIdx.x * 4; i < nt * KT; i += RN_RED_THREADS * 4) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int sl = 0; sl < p.nslices; ++sl) {
+                const float4 v = *reinterpret_cast<const float4 *>(src + sl * slice_stride + i);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            put(i, sum.x); put(i + 1, sum.y); put(i + 2, sum.z); put(i + 3, sum.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < nt * KT; i += RN_RED_THREADS) {
+            float sum = 0.f;
+#pragma unroll 8
+            for (int sl = 0; sl < p.nslices; ++sl) sum += src[sl * slice_stride + i];
+            put(i, sum);
+        }
     }
     __syncthreads();
     float *dst = bp.dval + b * bp.vb + h * bp.vh + int64_t(t0) * bp.vt;
