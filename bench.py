@@ -453,6 +453,9 @@ TWIN_SHAPES = {
     # name: (kind, B, T, H, U, P, K, C, dtype)
     "addr_U5P8_K8 (config-2 twin, 32768 slots)": ("addr", 8, 8192, 16, 5, 8, 8, 0, "bfloat16"),
     "prefill_U4P8_K16_C128 (config-3 twin, 4096 slots)": ("prefill", 4, 8192, 16, 4, 8, 16, 128, "bfloat16"),
+    "prefill_fwd_bwd_U4P8_K16_C128 (config-3 twin, forward + backward)": ("train", 4, 8192, 16, 4, 8, 16, 128, "bfloat16"),
+    "prefill_U4P8_K16_C128 at config-3 size (B8 T16384)": ("prefill", 8, 16384, 16, 4, 8, 16, 128, "bfloat16"),
+    "prefill_fwd_bwd_U4P8_K16_C128 at config-3 size (B8 T16384)": ("train", 8, 16384, 16, 4, 8, 16, 128, "bfloat16"),
     "decode_U4P8_K16_C128 (config-4 twin, 4096 slots)": ("decode", 64, 1, 16, 4, 8, 16, 128, "bfloat16"),
     "prefill_U4P4_K4_C64 (config-1 twin, 256 slots)": ("prefill", 1, 512, 4, 4, 4, 4, 64, "float32"),
 }
@@ -484,6 +487,15 @@ def twin_times(tag):
             if kind == "prefill":
                 def call():
                     return ro.random_access_memory_attention(k, q, v, gm, embed_num=E, top_k=K, impl_backend="cuda")
+            elif kind == "train":
+                leaves = [t.requires_grad_() for t in (q, k, v, gm)]
+                dy = torch.randn(B, T, H, C, device=device, generator=g).to(dtype)
+
+                def call():
+                    out = ro.random_access_memory_attention(k, q, v, gm, embed_num=E, top_k=K, impl_backend="cuda")
+                    (out[0] if isinstance(out, (tuple, list)) else out).backward(dy)
+                    for t in leaves:
+                        t.grad = None
             else:
                 slot = torch.randn(B, H, A, C, device=device, generator=g) * 0.1
                 mass = torch.rand(B, H, A, device=device, generator=g) + 0.1
@@ -496,16 +508,40 @@ def twin_times(tag):
             for _ in range(3):
                 call()
             torch.cuda.synchronize()
-            reps = 20 if kind != "prefill" or B * T < 10000 else 5
+            reps = 20 if kind not in ("prefill", "train") or B * T < 10000 else (5 if B * T < 100000 else 2)
+            run, how = None, "eager"
+            if kind != "train":
+                # forward-only shapes are replayed from a CUDA graph of `reps` calls: the small ones (one decode
+                # step, config 1) would otherwise measure the host's launch overhead, not the kernels
+                try:
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        call()
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        for _ in range(reps):
+                            call()
+                    run, how = graph.replay, "cuda_graph"
+                    run()
+                    torch.cuda.synchronize()
+                except Exception:  # noqa: BLE001
+                    torch.cuda.synchronize()
+                    run, how = None, "eager"
             times = []
             for _ in range(3):
                 e0.record()
-                for _ in range(reps):
-                    call()
+                if run is not None:
+                    run()
+                else:
+                    for _ in range(reps):
+                        call()
                 e1.record()
                 torch.cuda.synchronize()
                 times.append(e0.elapsed_time(e1) / reps)
             out[name] = median(times)
+            out[name + " timing"] = how
         except Exception as exc:  # noqa: BLE001
             out[name] = f"failed: {type(exc).__name__}: {exc}"[:160]
         del q, k
@@ -525,12 +561,14 @@ def run_twin():
         ref = json.loads(res.stdout.strip().splitlines()[-1])
     except Exception:  # noqa: BLE001
         return {"unavailable": "reference worker failed: " + (res.stderr or res.stdout)[-300:]}
-    twin = {"api": "ramnet_ops.random_access_memory_attention / topk_addr, impl_backend='cuda', CUDA events, median of 3",
+    twin = {"api": "ramnet_ops.random_access_memory_attention / topk_addr, impl_backend='cuda', CUDA events, median of 3; "
+                   "forward-only shapes replayed from a CUDA graph where the package allows capture, else eager",
             "reference_package": ref.get("package"), "our_package": ours.get("package")}
     for name in TWIN_SHAPES:
         a, b = ref.get(name), ours.get(name)
         twin[name] = {"reference_ms": a, "ours_ms": b,
-                      "speedup": (a / b) if isinstance(a, float) and isinstance(b, float) and b > 0 else None}
+                      "speedup": (a / b) if isinstance(a, float) and isinstance(b, float) and b > 0 else None,
+                      "timing": {"reference": ref.get(name + " timing"), "ours": ours.get(name + " timing")}}
     return twin
 
 

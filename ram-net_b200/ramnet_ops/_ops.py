@@ -316,6 +316,13 @@ def _gsu_forward_(addr_idx, addr_val, x, gamma, slot, mass, mask, w_top_k, r_top
     return gsu_forward_impl(addr_idx, addr_val, x, gamma, slot, mass, slot, mass, mask, w_top_k, r_top_k, mass_aware, eps)
 
 
+def _rows_as_given(t: torch.Tensor) -> torch.Tensor:
+    """(B,H,T,C) tensor as the backward kernels take it: any batch / head / token strides (a token-major tensor
+    seen head-major needs no copy), channels contiguous, rows aligned to four elements."""
+    ok = t.stride(-1) == 1 and all(st % 4 == 0 for st in t.stride()[:3]) and t.data_ptr() % (4 * t.element_size()) == 0
+    return t if ok else t.contiguous()
+
+
 def _pad_channels(t: torch.Tensor, C4: int) -> torch.Tensor:
     C = t.shape[-1]
     return t if C == C4 else torch.nn.functional.pad(t, (0, C4 - C))
@@ -332,14 +339,14 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
     C4 = (C + 3) // 4 * 4  # the kernels move channels in groups of four
     if addr_val.stride() != addr_idx.stride():
         addr_idx, addr_val = addr_idx.contiguous(), addr_val.contiguous()
-    xs = _pad_channels(x, C4).contiguous()
-    dy = _pad_channels(D_y.to(x.dtype), C4).contiguous()
+    xs = _rows_as_given(_pad_channels(x, C4))
+    dy = _rows_as_given(_pad_channels(D_y.to(x.dtype), C4))
     slot_in = _pad_channels(init_slot.to(torch.float32), C4).contiguous()
     mass_in = init_mass.to(torch.float32).contiguous()
     d_slot_post = _pad_channels(D_post_slot.to(torch.float32), C4).contiguous()
     d_mass_post = D_post_mass.to(torch.float32).contiguous()
     d_val = torch.zeros((B, T, H, K), dtype=torch.float32, device=x.device).permute(0, 2, 3, 1)
-    d_x = torch.empty_like(xs)
+    d_x = torch.empty(xs.shape, dtype=xs.dtype, device=xs.device)
     d_gamma = torch.empty((B, H, T), dtype=torch.float32, device=x.device)
     d_slot, d_mass = torch.empty_like(slot_in), torch.empty_like(mass_in)
     if x.numel() == 0:
