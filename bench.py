@@ -735,6 +735,19 @@ def run_ncu_case(name):
             idx, val = ops.topk_addr_forward(k.permute(0, 2, 3, 4, 1), q.permute(0, 2, 3, 4, 1), E, A, pos, K, K, 0.0, 0.0)
             y, s1, m1 = ops.gsu_forward(idx, val, v.permute(0, 2, 1, 3), gm.permute(0, 2, 1), slot0, mass0, None, K, K, False, 1e-12)
         out = float(y.float().abs().mean())
+    elif name == "prefill_bwd_small":
+        # forward + backward of the model shape at B2 T4096 (3.3 GB of backward workspace), two passes
+        B, T, H, U, P, K, C, E = 2, 4096, 16, 2, 64, 16, 128, 8
+        A = P ** U
+        q = torch.randn(B, T, H, U, P, device=device, generator=g).bfloat16().requires_grad_()
+        k = torch.randn(B, T, H, U, P, device=device, generator=g).bfloat16().requires_grad_()
+        v = torch.randn(B, T, H, C, device=device, generator=g).bfloat16().requires_grad_()
+        gm = torch.sigmoid(torch.randn(B, T, H, device=device, generator=g) + 1).bfloat16().requires_grad_()
+        dy = torch.randn(B, T, H, C, device=device, generator=g).bfloat16()
+        for _ in range(2):
+            y = ramnet_ops.random_access_memory_attention(k, q, v, gm, embed_num=E, top_k=K, impl_backend="cuda")
+            (y[0] if isinstance(y, (tuple, list)) else y).backward(dy)
+        out = float(v.grad.float().abs().mean())
     elif name == "decode_small":
         B, H, U, P, K, C, E = 64, 16, 2, 64, 16, 128, 8
         A = P ** U
@@ -792,7 +805,7 @@ def main():
     ap.add_argument("--no-full-model", action="store_true", help="skip the full language-model run")
     ap.add_argument("--no-twin", action="store_true", help="skip the twin-shape comparison with the reference's CUDA kernels")
     ap.add_argument("--twin-ref-worker", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--ncu-case", default=None, choices=["prefill_small", "prefill_full", "decode_small", "addr_small"],
+    ap.add_argument("--ncu-case", default=None, choices=["prefill_small", "prefill_full", "prefill_bwd_small", "decode_small", "addr_small"],
                     help="run one small case of the kernels (for profiler captures) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

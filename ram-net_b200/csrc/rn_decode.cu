@@ -703,9 +703,12 @@ static int rn_launch_decode_pair(const RnDecodeParams &p, int device, cudaStream
         if (p.C != 128 && p.C != 256) return -1;
         const int threads = p.C == 128 ? RnDecPair<1>::THREADS : RnDecPair<2>::THREADS;
         const int wpc = threads / 32;
-        const int want = (p.B * p.H + wpc - 1) / wpc;
-        const int cap = 2 * rn_sm_count(device);  // two resident CTAs per SM; the warps stride over the pairs
-        const int grid = want < cap ? want : cap;
+        // CTAs: enough for one warp per pair, but at least one per SM while there are pairs to hand out (a small
+        // batch is spread over all SMs instead of filling a few), at most the two resident CTAs per SM
+        const int sms = rn_sm_count(device), pairs = p.B * p.H;
+        int grid = (pairs + wpc - 1) / wpc;
+        if (grid < sms) grid = pairs < sms ? pairs : sms;
+        if (grid > 2 * sms) grid = 2 * sms;
         if (p.C == 128) {
             constexpr int smem = (RnDecPair<1>::THREADS / 32) * 16 * 128 * 4;
             if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
