@@ -12,9 +12,7 @@ template <typename T, bool SMEM_TABLES, int EPT>
 __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(const RnGsuParams p) {
     const int NT = blockDim.x;  // threads of this CTA: EPT * NT >= events per chunk
     extern __shared__ __align__(16) unsigned char dyn[];
-    __shared__ float gam[2][RN_GSU_LMAX];
     __shared__ float tok_scale[RN_GSU_LMAX];
-    __shared__ unsigned char tok_live[2][RN_GSU_LMAX];
     __shared__ int n_heads, n_rheads;
 
     const int bh = blockIdx.x;
@@ -67,9 +65,12 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     const T *gamma = static_cast<const T *>(p.gamma) + b * p.gb + h * p.gh;
     const int64_t ibase = b * p.ib + h * p.ih;
 
-    // software pipeline: the raw idx / val of the next chunk are loaded while this one is resolved
+    // software pipeline: what the next chunk needs from global memory is requested while this one is resolved and
+    // waits in registers: per event the raw idx / val and its token's gamma and mask byte (a warp's events share
+    // few tokens, so these are broadcast loads)
     int nraw[EPT];
-    float nval[EPT];
+    float nval[EPT], ngam[EPT];
+    bool nlive[EPT];
     auto prefetch = [&](int chunk) {
         const int t0 = chunk * p.L;
         const int Lc = min(p.L, p.T - t0);
@@ -77,15 +78,15 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         for (int j = 0; j < EPT; ++j) {
             nraw[j] = 0;
             nval[j] = 0.f;
+            ngam[j] = 0.f;
+            nlive[j] = false;
             if (chunk < p.nchunks && ev_t[j] < Lc) {
                 const int64_t o = ibase + int64_t(ev_k[j]) * p.ik + int64_t(t0 + ev_t[j]) * p.it;
                 nraw[j] = p.idx[o];
                 nval[j] = p.val[o];
+                ngam[j] = rn_to_float<T>(gamma[(t0 + ev_t[j]) * p.gt]);
+                nlive[j] = p.mask ? p.mask[b * p.mb + (t0 + ev_t[j]) * p.mt] != 0 : true;
             }
-        }
-        if (chunk < p.nchunks && tid < Lc) {
-            gam[chunk & 1][tid] = rn_to_float<T>(gamma[(t0 + tid) * p.gt]);
-            tok_live[chunk & 1][tid] = p.mask ? p.mask[b * p.mb + (t0 + tid) * p.mt] : 1;
         }
     };
     prefetch(0);
@@ -94,12 +95,11 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
     for (int chunk = 0; chunk < p.nchunks; ++chunk) {
         const int t0 = chunk * p.L;
         const int Lc = min(p.L, p.T - t0);
-        const float *g_cur = gam[chunk & 1];
-        const unsigned char *live_cur = tok_live[chunk & 1];
 
         // ---- this thread's events ---------------------------------------------------------------
         uint32_t ea[EPT];
         float ev[EPT], ec[EPT], em[EPT];  // slot, weight, coefficient, mass before the write
+        float alpha[EPT], mnew[EPT];      // writes: forgetting factor (needs no mass: computed up front), mass after
         int er[EPT];          // round, or -1 dead (zero weight / masked token), -3 out of range
         uint32_t pend = 0;
         if (tid == 0) {
@@ -113,8 +113,12 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
             em[j] = 0.f;
             ea[j] = pow2 ? uint32_t(nraw[j] & (A - 1)) : uint32_t(nraw[j] % A);
             ev[j] = fabsf(nval[j]);
+            mnew[j] = 0.f;
+            // outside the rounds on purpose: there the lanes of a warp win at different times, and everything
+            // inside is paid once per round by the whole warp
+            alpha[j] = ev_k[j] < p.Kw ? rn_alpha(ev[j], ngam[j]) : 0.f;
             if (ev_t[j] < Lc) {
-                const bool live = live_cur[ev_t[j]] && ev[j] != 0.f;
+                const bool live = nlive[j] && ev[j] != 0.f;
                 er[j] = live ? 0 : -1;
                 if (live) pend |= 1u << j;
             }
@@ -138,9 +142,8 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
                 if (claim[ea[j]] == uint32_t(j * NT + tid)) {
                     if (ev_k[j] < p.Kw) {
                         em[j] = mass[ea[j]];
-                        const RnGate g = rn_gate(ev[j], g_cur[ev_t[j]], em[j], p.eps);
-                        mass[ea[j]] = g.mass;
-                        ec[j] = g.gain;
+                        mnew[j] = fmaf(alpha[j], em[j], ev[j]);  // rn_gate(): mass' = alpha * mass + w
+                        mass[ea[j]] = mnew[j];
                     } else {
                         em[j] = mass[ea[j]];
                         ec[j] = p.mass_aware ? ev[j] * em[j] : ev[j];
@@ -161,6 +164,10 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
             ++R;
             if (!__syncthreads_or(pend != 0)) break;
         }
+        // the gains of the writes, rn_gate(): gain = w / (mass' + eps)
+#pragma unroll
+        for (int j = 0; j < EPT; ++j)
+            if (er[j] >= 0 && ev_k[j] < p.Kw) ec[j] = ev[j] / (mnew[j] + p.eps);
 
         // ---- mass-aware reads: y_t = sum_k (r m slot) * sum r / (sum r m + eps) -------------------
         if (p.mass_aware) {
