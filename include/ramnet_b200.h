@@ -201,7 +201,9 @@ int rn_gsu_fwd(const int32_t *idx, const float *val, const int64_t *idx_strides,
  *  d_x          : output (B,H,T,C) in the dtype of x;  d_gamma: (B,H,T) float32 contiguous;
  *  d_slot, d_mass : gradients of the initial state, float32 contiguous.
  *  workspace    : rn_gsu_bwd_workspace_bytes(...) bytes, 256-byte aligned (per write event it holds
- *                 x - slot_before, C floats, like the reference's replay cache).
+ *                 x - slot_before, C floats, like the reference's replay cache, laid out per channel
+ *                 slice; per event and channel slice one partial dot product; the event schedule).
+ *                 Results are run-to-run deterministic: no float atomics are used.
  * Needs C % 4 == 0, A <= 65536 and a channel slice of the state that fits shared memory.
  */
 int64_t rn_gsu_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t A, int64_t C, int64_t Kw, int64_t Kr,
