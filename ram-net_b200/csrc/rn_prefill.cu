@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(RN_SCHED_THREADS_MAX) rn_gsu_schedule_kernel(c
         uint16_t *o_heads = reinterpret_cast<uint16_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 16);
         uint32_t *o_slot = reinterpret_cast<uint32_t *>(rec + RN_GSU_HDR_BYTES + size_t(NEp) * 17 + 16);
         if (tid == 0) reinterpret_cast<uint32_t *>(rec)[0] = uint32_t(R);
-        // chain heads (round-1 events) in any order: warp-aggregated append
+        // chain heads (the events that retired in the second claim round, er == 1) in any order: warp-aggregated append
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             const bool emit = er[j] == 1;

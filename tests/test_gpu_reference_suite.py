@@ -7,7 +7,8 @@ behaviour (chunked == full, in place == functional, masks) and numerics against 
 with --bf16 --fp16, in the 16-bit types.  This test runs that suite in a subprocess with this package first on the
 import path.  It needs a checkout of the reference, which is not part of this repository: set the environment
 variable RAMNET_REFERENCE_ROOT to a directory that holds the reference's ``tests`` package; without it the test is
-skipped.  tests/reference_suite_result.md holds the result of the last run on a B200.
+skipped.  RAMNET_REFERENCE_SUITE_LOG names a file that receives the suite's full output.
+tests/reference_suite_result.md holds the result of the last run on a B200.
 """
 import os
 import subprocess
@@ -32,8 +33,8 @@ def test_reference_operator_suite_passes_unmodified():
     res = subprocess.run([sys.executable, "-m", "tests", "--part", "ops", "--device", "cuda", "--bf16", "--fp16", "--seeds", *seeds],
                          cwd=ref_root, env=env, capture_output=True, text=True, timeout=3000)
     log = res.stdout + res.stderr
-    out_dir = ROOT / "gpurun_out"
-    if out_dir.exists():
-        (out_dir / "reference_suite.log").write_text(log)
+    log_path = os.environ.get("RAMNET_REFERENCE_SUITE_LOG", "")
+    if log_path:
+        Path(log_path).write_text(log)
     assert "ram-net_b200" in log, "the suite must have imported this package, not the reference's"
     assert res.returncode == 0, "reference suite failed:\n" + log[-4000:]
