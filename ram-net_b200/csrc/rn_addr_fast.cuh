@@ -259,11 +259,25 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
 
     auto digit = [&](const int u) __attribute__((always_inline)) {
         // ---- digit u: keys, log-sum-exp, sorted Top-K -------------------------------------------
-        // three passes over the row's P logits (L1-resident after the first): max, sum of
-        // exponentials, keys; nothing but the keys stays in registers
+        // Passes over the row's P logits (L1-resident after the first); nothing but the keys stays in registers.
+        // Rolled digit loop (three or more digits): keys, then the sum of exponentials; the maximum the sum needs is
+        // the value of the best key (8 % faster at U = 3, P = 32, K = 8).  Unrolled (two digits of 64 logits): a
+        // maximum pass first, the keys last, which keeps the 64 keys out of the way of the exponentials (the
+        // two-pass order is 2.5 % slower there).
+        constexpr bool MAX_FROM_KEYS = U >= 3;
         DKey dk[P];
         float xmax = -INFINITY;
-        rn_for_each_logit<T, P>(src + u * P, [&](int, float x) { xmax = fmaxf(xmax, x); });
+        auto sort_keys = [&]() __attribute__((always_inline)) {
+            rn_make_keys<T, P>(src + u * P, dk);
+            static_for<0, NB>([&](auto BI) __attribute__((always_inline)) { oem_sort_desc<KD>(dk + decltype(BI)::value * KD); });
+            static_for<1, NB>([&](auto BI) __attribute__((always_inline)) { fold_topk<KD>(dk, dk + decltype(BI)::value * KD); });
+        };
+        if constexpr (MAX_FROM_KEYS) {
+            sort_keys();
+            xmax = digit_value<T>(dk[0]);
+        } else {
+            rn_for_each_logit<T, P>(src + u * P, [&](int, float x) { xmax = fmaxf(xmax, x); });
+        }
         if (xmax == -INFINITY) {
             inactive = true;
         } else {
@@ -272,9 +286,7 @@ __device__ __forceinline__ void thread_decode(const T *src, const float rho, int
             rn_for_each_logit<T, P>(src + u * P, [&](int, float x) { s += fast_ex2(fmaf(x, LOG2E, -off)); });
             lse_total += xmax + fast_lg2(s) * LN2;
         }
-        rn_make_keys<T, P>(src + u * P, dk);
-        static_for<0, NB>([&](auto BI) __attribute__((always_inline)) { oem_sort_desc<KD>(dk + decltype(BI)::value * KD); });
-        static_for<1, NB>([&](auto BI) __attribute__((always_inline)) { fold_topk<KD>(dk, dk + decltype(BI)::value * KD); });
+        if constexpr (!MAX_FROM_KEYS) sort_keys();
         // dk[0..KD) = this digit's KD best logits, sorted descending
 
         if (u == 0) {
