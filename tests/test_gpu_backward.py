@@ -115,3 +115,24 @@ def test_all_masked_gradients_are_identity():
         assert float(gr.abs().max()) == 0.0
     for gr in grads[4:]:
         assert torch.equal(gr, torch.ones_like(gr))
+
+
+def test_gradients_are_bitwise_reproducible():
+    """No float atomics on the backward path: two runs on the same inputs give the same bits (the model shape in
+    bf16, chunks with chains, two batch rows, CAPE on half of the heads)."""
+    ops()
+    B, H, U, P, T, C, K = 2, 4, 2, 64, 200, 128, (16, 16)
+    w = randn((B, T, H, U, P), 21, torch.float32, 1.5)
+    r = randn((B, T, H, U, P), 22, torch.float32, 1.5)
+    x = randn((B, T, H, C), 23)
+    g = torch.sigmoid(randn((B, T, H), 24))
+    A = P ** U
+    slot, mass = randn((B, H, A, C), 25) * 0.1, torch.rand(B, H, A, generator=torch.Generator().manual_seed(26)) * 0.5
+    pos = torch.arange(T).view(1, T).expand(B, T).contiguous()
+    d_y, d_slot, d_mass = randn((B, T, H, C), 27), randn((B, H, A, C), 28) * 0.1, randn((B, H, A), 29) * 0.1
+    runs = [run_api(w, r, x, g, slot, mass, None, pos, H // 2, K, (0.0, 0.0), 1e-6, d_y, d_slot, d_mass, torch.bfloat16)
+            for _ in range(2)]
+    for a, b in zip(runs[0][0], runs[1][0]):
+        assert torch.equal(a, b)
+    for name, a, b in zip(("D_w", "D_r", "D_x", "D_gamma", "D_slot", "D_mass"), runs[0][1], runs[1][1]):
+        assert torch.equal(a, b), f"{name}: {int((a != b).sum())} elements differ between two runs"
