@@ -346,11 +346,11 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
     d_slot_post = _pad_channels(D_post_slot.to(torch.float32), C4).contiguous()
     d_mass_post = D_post_mass.to(torch.float32).contiguous()
     d_val = torch.zeros((B, T, H, K), dtype=torch.float32, device=x.device).permute(0, 2, 3, 1)
-    d_x = torch.empty(xs.shape, dtype=xs.dtype, device=xs.device)
+    d_x = torch.empty_like(xs)  # in the layout of x: a token-major x gets a token-major gradient, which autograd can hand on as it is
     d_gamma = torch.empty((B, H, T), dtype=torch.float32, device=x.device)
     d_slot, d_mass = torch.empty_like(slot_in), torch.empty_like(mass_in)
     if x.numel() == 0:
-        return d_val, d_x[..., :C].contiguous(), d_gamma, d_slot_post[..., :C].clone(), d_mass_post.clone()
+        return d_val, torch.empty_like(x), d_gamma, d_slot_post[..., :C].clone(), d_mass_post.clone()
     mask_u8 = None if mask is None else mask.to(torch.bool).view(torch.uint8)
     nbytes = lib.rn_gsu_bwd_workspace_bytes(B, H, T, A, C4, w_top_k, r_top_k, x.device.index)
     if nbytes < 0:
@@ -363,7 +363,7 @@ def _gsu_backward(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y,
                          C4, w_top_k, r_top_k, int(mass_aware), float(eps), x.device.index, stream_of(x)))
     check_device(d_val)
     if C4 != C:  # results of the padded run: hand back dense tensors, as the fake kernel promises
-        return d_val, d_x[..., :C].contiguous(), d_gamma, d_slot[..., :C].contiguous(), d_mass
+        return d_val, torch.empty_like(x).copy_(d_x[..., :C]), d_gamma, d_slot[..., :C].contiguous(), d_mass
     return d_val, d_x, d_gamma, d_slot, d_mass
 
 
@@ -453,4 +453,4 @@ def _topk_segment_backward(seg_idx, seg_off, seg_len, event_i, event_v, x, gamma
                                       init_slot.shape[2])
     d_val, d_x, d_gamma, d_slot, d_mass = _gsu_backward(idx, val, x, gamma, init_slot, init_mass, None, D_y.to(x.dtype),
                                                         D_post_slot, D_post_mass, w_top_k, r_top_k, mass_aware, eps)
-    return d_val.contiguous(), d_x.to(torch.float32), d_gamma, d_slot, d_mass
+    return d_val.contiguous(), d_x.to(torch.float32).contiguous(), d_gamma, d_slot, d_mass

@@ -121,7 +121,7 @@ def _(addr_idx, addr_val, x, gamma, slot, mass, mask, w_top_k, r_top_k, mass_awa
 def _(addr_idx, addr_val, x, gamma, init_slot, init_mass, mask, D_y, D_post_slot, D_post_mass, w_top_k, r_top_k,
       mass_aware, eps):
     B, H, T, C = x.shape
-    return (_token_major(x, B, H, w_top_k + r_top_k, T, torch.float32), x.new_empty(x.shape),
+    return (_token_major(x, B, H, w_top_k + r_top_k, T, torch.float32), torch.empty_like(x),
             x.new_empty((B, H, T), dtype=torch.float32), init_slot.new_empty(init_slot.shape, dtype=torch.float32),
             init_mass.new_empty(init_mass.shape, dtype=torch.float32))
 
@@ -186,7 +186,7 @@ def _(seg_idx, seg_off, seg_len, event_i, event_v, x, gamma, init_slot, init_mas
     d_slot = init_slot.new_empty(init_slot.shape, dtype=torch.float32)
     d_mass = init_mass.new_empty(init_mass.shape, dtype=torch.float32)
     if _direct(seg_off):
-        return (_token_major(x, B, H, K, T, torch.float32), x.new_empty(x.shape), x.new_empty((B, H, T), dtype=torch.float32),
+        return (_token_major(x, B, H, K, T, torch.float32), torch.empty_like(x), x.new_empty((B, H, T), dtype=torch.float32),
                 d_slot, d_mass)
     return (x.new_empty((B, H, K, T), dtype=torch.float32), x.new_empty(x.shape, dtype=torch.float32),
             gamma.new_empty(gamma.shape, dtype=torch.float32), d_slot, d_mass)
