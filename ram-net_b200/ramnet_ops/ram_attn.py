@@ -211,10 +211,15 @@ def random_access_memory_attention(
     # defaults
     if not isinstance(gamma, T_):
         gamma = values.new_full((*batch_shape, H, 1), gamma).expand(*batch_shape, H, T)
+    # A default state is created in the dtype the CUDA backend keeps state in (float32 for 16-bit values), so that
+    # the backend does not convert a fresh 16-bit tensor of A*C zeros per head first
+    state_dtype = values.dtype
+    if impl_backend in (None, 'cuda') and values.is_cuda and values.dtype in (torch.float16, torch.bfloat16):
+        state_dtype = torch.float32
     if not isinstance(init_slot, T_):
-        init_slot = values.new_zeros(*batch_shape, H, A, C)
+        init_slot = values.new_zeros(*batch_shape, H, A, C, dtype=state_dtype)
     if not isinstance(init_mass, T_):
-        init_mass = values.new_full((*batch_shape, H, A), 1.0 / (P ** U) if init_mass is None else init_mass)
+        init_mass = values.new_full((*batch_shape, H, A), 1.0 / (P ** U) if init_mass is None else init_mass, dtype=state_dtype)
     if not isinstance(position_ids, T_):
         position_ids = torch.arange(T, device=values.device, dtype=torch.long).view(*([1] * len(batch_shape)), T)
     else:
