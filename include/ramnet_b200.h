@@ -135,6 +135,23 @@ int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const 
                    int mass_aware, double eps, int device, void *stream);
 
 /*
+ * The same step with the layer's address scaling folded into the load of the logits
+ * (packages/ramnet/src/ramnet/layers/ram_attn_block.py:314-315: logits * exp(scale) / temperature):
+ *  w_scale, r_scale : (H,U) factors in dtype, both or neither; a logit enters the decode as
+ *                     round_to_dtype(factor * logit), exactly what the separate multiply produces.
+ * Taken where rn_decode_scales_supported() returns 1 (16-bit logits, U=2, P=64, Kw=Kr=16, C in {128, 256});
+ * elsewhere the call fails and the caller multiplies beforehand.
+ */
+int rn_decode_scales_supported(int dtype, int64_t U, int64_t P, int64_t C, int64_t Kw, int64_t Kr);
+int rn_decode_step_scaled(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
+                          float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
+                          const float *norm_weight, const void *gate_logits, double norm_eps,
+                          const void *w_scale, const void *r_scale,
+                          int64_t B, int64_t H, int64_t U, int64_t P, int64_t C, int64_t E,
+                          int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
+                          int mass_aware, double eps, int device, void *stream);
+
+/*
  * Prefill (T > 1) gated sparse update + read over decoded addresses.
  * Replaces gather_segment + ramnet_ops::topk_segment_forward / topk_segment_forward_
  * (packages/ramnet-ops/src/ramnet_ops/impl/cuda_impl.py:72-141,

@@ -107,6 +107,20 @@ __device__ __forceinline__ float4 rn_cvt_raw4(const RnRaw4<__nv_bfloat16> &r) {
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.v.y));
     return make_float4(a.x, a.y, b.x, b.y);
 }
+// four floats rounded to the 16-bit type, packed as rn_load_raw4 delivers them
+template <typename T> __device__ __forceinline__ RnRaw4<T> rn_pack_raw4(float4 v);
+template <> __device__ __forceinline__ RnRaw4<__half> rn_pack_raw4<__half>(float4 v) {
+    RnRaw4<__half> r;
+    *reinterpret_cast<__half2 *>(&r.v.x) = __floats2half2_rn(v.x, v.y);
+    *reinterpret_cast<__half2 *>(&r.v.y) = __floats2half2_rn(v.z, v.w);
+    return r;
+}
+template <> __device__ __forceinline__ RnRaw4<__nv_bfloat16> rn_pack_raw4<__nv_bfloat16>(float4 v) {
+    RnRaw4<__nv_bfloat16> r;
+    *reinterpret_cast<__nv_bfloat162 *>(&r.v.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162 *>(&r.v.y) = __floats2bfloat162_rn(v.z, v.w);
+    return r;
+}
 template <typename T> __device__ __forceinline__ void rn_store4(T *p, float4 v);
 template <> __device__ __forceinline__ void rn_store4<float>(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
 template <> __device__ __forceinline__ void rn_store4<__half>(__half *p, float4 v) {

@@ -31,6 +31,7 @@ struct RnDecodeParams {
     void *y;
     const float *norm_weight;
     const void *gate;
+    const void *scale[2];  // optional (H,U) factors of the write / read logits, in the dtype of the logits
     float norm_eps;
     int B, H, U, P, C, E, A;
     int K[2];
@@ -516,7 +517,19 @@ __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p,
         // ---- both addresses of the pair --------------------------------------------------------------
         int content;
         float weight;
-        rn_half::decode_u2p64k16<T>(logits, p.re_norm[which], lane, cand, content, weight);
+        uint2 scaled[2] = {logits[0], logits[1]};
+        if (p.scale[which] != nullptr) {
+            // the layer's learned scale over the temperature, one factor per (head, digit): the product is rounded
+            // to the dtype of the logits, as the separate elementwise multiply of the layer code rounds it
+            const T *sc = static_cast<const T *>(p.scale[which]) + h * U;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float f = rn_to_float<T>(sc[u]);
+                const float4 v = rn_cvt_raw4(RnRaw4<T>{scaled[u]});
+                scaled[u] = rn_pack_raw4<T>(make_float4(v.x * f, v.y * f, v.z * f, v.w * f)).v;
+            }
+        }
+        rn_half::decode_u2p64k16<T>(scaled, p.re_norm[which], lane, cand, content, weight);
         const int my_slot = rn_cape(content, shift, p.A);
         // lanes 0-15: entry `lane` of the write address; their read entry comes from the upper half
         const int a_l = my_slot;
@@ -774,12 +787,37 @@ static int rn_launch_decode(const RnDecodeParams &p, int kpl, int ppl, int grid,
     return 1;
 }
 
+extern "C" int rn_decode_step_scaled(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
+                                     float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
+                                     const float *norm_weight, const void *gate_logits, double norm_eps,
+                                     const void *w_scale, const void *r_scale, int64_t B, int64_t H, int64_t U, int64_t P,
+                                     int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
+                                     int mass_aware, double eps, int device, void *stream);
+
+// 1 when rn_decode_step_scaled() takes logit scales for this shape (the one-warp-per-pair kernel does), else 0
+extern "C" int rn_decode_scales_supported(int dtype, int64_t U, int64_t P, int64_t C, int64_t Kw, int64_t Kr) {
+    return (dtype == RN_F16 || dtype == RN_BF16) && U == 2 && P == 64 && Kw == 16 && Kr == 16 && (C == 128 || C == 256);
+}
+
 extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
                               float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
                               const float *norm_weight, const void *gate_logits, double norm_eps, int64_t B, int64_t H,
                               int64_t U, int64_t P, int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm,
                               double r_re_norm, int mass_aware, double eps, int device, void *stream) {
+    return rn_decode_step_scaled(w_addr, r_addr, x, gamma, dtype, slot, mass, mask, pos, y, norm_weight, gate_logits, norm_eps,
+                                 nullptr, nullptr, B, H, U, P, C, E, Kw, Kr, w_re_norm, r_re_norm, mass_aware, eps, device, stream);
+}
+
+extern "C" int rn_decode_step_scaled(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
+                                     float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
+                                     const float *norm_weight, const void *gate_logits, double norm_eps,
+                                     const void *w_scale, const void *r_scale, int64_t B, int64_t H, int64_t U, int64_t P,
+                                     int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
+                                     int mass_aware, double eps, int device, void *stream) {
     rn_clear_error();
+    RN_REQUIRE((w_scale == nullptr) == (r_scale == nullptr), "give both logit scales or none");
+    RN_REQUIRE(w_scale == nullptr || rn_decode_scales_supported(dtype, U, P, C, Kw, Kr),
+               "logit scales are taken for 16-bit logits with U=2, P=64, K=16, C in {128, 256} only");
     RN_REQUIRE(w_addr && r_addr && x && gamma && slot && mass && pos && y, "null pointer argument");
     RN_REQUIRE(B > 0 && H > 0 && U > 0 && P > 0 && C > 0, "decode dims must be positive");
     RN_REQUIRE(U <= RN_UMAX, "Expect U <= %d but got %lld", RN_UMAX, (long long)U);
@@ -805,6 +843,7 @@ extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void
     p.w_addr = w_addr; p.r_addr = r_addr; p.x = x; p.gamma = gamma;
     p.slot = slot; p.mass = mass; p.mask = mask; p.pos = pos; p.y = y;
     p.norm_weight = norm_weight; p.gate = gate_logits; p.norm_eps = float(norm_eps);
+    p.scale[0] = w_scale; p.scale[1] = r_scale;
     p.B = int(B); p.H = int(H); p.U = int(U); p.P = int(P); p.C = int(C); p.E = int(E); p.A = int(A);
     p.K[0] = int(Kw); p.K[1] = int(Kr);
     p.re_norm[0] = float(w_re_norm); p.re_norm[1] = float(r_re_norm);

@@ -35,7 +35,8 @@ _lib.define(
 _lib.define(
     "decode_fused_(Tensor w_addr, Tensor r_addr, Tensor x, Tensor gamma, Tensor(a!) slot, Tensor(b!) mass, "
     "Tensor mask, int embed_num, Tensor position_ids, int w_top_k, int r_top_k, float w_re_norm, float r_re_norm, "
-    "bool mass_aware, float eps, Tensor? norm_weight, Tensor? gate_logits, float norm_eps) -> Tensor")
+    "bool mass_aware, float eps, Tensor? norm_weight, Tensor? gate_logits, float norm_eps, "
+    "Tensor? w_scale=None, Tensor? r_scale=None) -> Tensor")
 _lib.define(
     "gsu_forward(Tensor addr_idx, Tensor addr_val, Tensor x, Tensor gamma, Tensor init_slot, Tensor init_mass, "
     "Tensor? mask, int w_top_k, int r_top_k, bool mass_aware, float eps) -> (Tensor, Tensor, Tensor)")
@@ -204,8 +205,16 @@ def _topk_addr_backward(idx, val, w_addr, r_addr, D_val, embed_num, position_ids
 # ----------------------------------------------------------------------------------------------
 # fused decode step
 # ----------------------------------------------------------------------------------------------
+def decode_scales_supported(dtype, U, P, C, w_top_k, r_top_k) -> bool:
+    from ._C import DTYPE_CODE
+    code = DTYPE_CODE.get(dtype)
+    return code is not None and bool(lib.rn_decode_scales_supported(code, U, P, C, w_top_k, r_top_k))
+
+
 def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
-                r_re_norm, mass_aware, eps, norm_weight=None, gate_logits=None, norm_eps=0.0):
+                r_re_norm, mass_aware, eps, norm_weight=None, gate_logits=None, norm_eps=0.0, w_scale=None, r_scale=None):
+    """One decode step.  ``w_scale`` / ``r_scale`` (H,U) or (H,U,1): factors of the logits, applied inside the
+    kernel where decode_scales_supported() says so, else by a multiply here (same rounding either way)."""
     _require_cuda(w_addr, r_addr, x, gamma, slot, mass, position_ids)
     B, H, U, P = w_addr.shape
     C = x.shape[-1]
@@ -215,6 +224,14 @@ def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_
         raise RuntimeError("Tensor slot/mass must be contiguous")
     if tuple(slot.shape) != (B, H, P ** U, C) or tuple(mass.shape) != (B, H, P ** U):
         raise RuntimeError(f"state shape mismatch: slot {tuple(slot.shape)}, mass {tuple(mass.shape)}")
+    if (w_scale is None) != (r_scale is None):
+        raise RuntimeError("give both logit scales or none")
+    if w_scale is not None:
+        w_scale = w_scale.to(w_addr.dtype).reshape(H, U).contiguous()
+        r_scale = r_scale.to(r_addr.dtype).reshape(H, U).contiguous()
+        if not decode_scales_supported(w_addr.dtype, U, P, C, w_top_k, r_top_k):
+            w_addr, r_addr = w_scale.unsqueeze(-1) * w_addr, r_scale.unsqueeze(-1) * r_addr
+            w_scale = r_scale = None
     w_addr, r_addr, x, gamma = (t.contiguous() for t in (w_addr, r_addr, x, gamma))
     if not (r_addr.dtype == x.dtype == gamma.dtype == w_addr.dtype):
         raise RuntimeError("w_addr, r_addr, x and gamma must share one dtype")
@@ -229,10 +246,11 @@ def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_
     y = torch.empty_like(x)
     if y.numel() == 0:
         return y
-    check(lib.rn_decode_step(ptr(w_addr), ptr(r_addr), ptr(x), ptr(gamma), dtype_code(x), ptr(slot), ptr(mass),
-                             ptr(mask_u8), ptr(pos), ptr(y), ptr(norm_weight), ptr(gate_logits), float(norm_eps),
-                             B, H, U, P, C, embed_num, w_top_k, r_top_k, float(w_re_norm), float(r_re_norm),
-                             int(mass_aware), float(eps), x.device.index, stream_of(x)))
+    check(lib.rn_decode_step_scaled(ptr(w_addr), ptr(r_addr), ptr(x), ptr(gamma), dtype_code(x), ptr(slot), ptr(mass),
+                                    ptr(mask_u8), ptr(pos), ptr(y), ptr(norm_weight), ptr(gate_logits), float(norm_eps),
+                                    ptr(w_scale), ptr(r_scale), B, H, U, P, C, embed_num, w_top_k, r_top_k,
+                                    float(w_re_norm), float(r_re_norm), int(mass_aware), float(eps), x.device.index,
+                                    stream_of(x)))
     check_device(y)
     return y
 
@@ -246,9 +264,9 @@ def _topk_autoregressive_(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num,
 
 @torch.library.impl(_lib, "decode_fused_", "CUDA")
 def _decode_fused_(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm,
-                   r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps):
+                   r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps, w_scale=None, r_scale=None):
     return decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k,
-                       w_re_norm, r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps)
+                       w_re_norm, r_re_norm, mass_aware, eps, norm_weight, gate_logits, norm_eps, w_scale, r_scale)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -96,7 +96,7 @@ def _(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top
 
 @torch.library.register_fake("ramnet_ops::decode_fused_")
 def _(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_ids, w_top_k, r_top_k, w_re_norm, r_re_norm,
-      mass_aware, eps, norm_weight, gate_logits, norm_eps):
+      mass_aware, eps, norm_weight, gate_logits, norm_eps, w_scale=None, r_scale=None):
     return x.new_empty(x.shape)
 
 

@@ -63,6 +63,31 @@ def fused_attention_class():
                 return False
             return hidden_states.dtype in (torch.float32, torch.float16, torch.bfloat16)
 
+        def _step_constants(self, what, dtype, device, B):
+            """Per-step tensors that depend on parameters only, computed as the parent class computes them and kept
+            until a parameter changes (in-place updates bump ``_version``; a new tensor has a new ``data_ptr``):
+            the learned address scales over the temperature, (H,U,1) each, and gamma expanded to (B,H).  One token
+            step then multiplies and launches, instead of re-deriving them with half a dozen small kernels."""
+            params = [p for p in (self.r_scale, self.w_scale, getattr(self, "gamma_modifier", None),
+                                  getattr(getattr(self, "gamma_modifier", None), "bias", None)) if isinstance(p, torch.Tensor)]
+            key = (what, dtype, device, B, float(self.addr_temperature), tuple((p.data_ptr(), p._version) for p in params))
+            cache = self.__dict__.setdefault("_rn_step_cache", {})
+            hit = cache.get(what)
+            if hit is not None and hit[0] == key:
+                return hit[1]
+            with torch.no_grad():
+                if what == "scales":
+                    value = ((torch.exp(self.r_scale) / self.addr_temperature).to(dtype=dtype).unsqueeze(-1).contiguous(),
+                             (torch.exp(self.w_scale) / self.addr_temperature).to(dtype=dtype).unsqueeze(-1).contiguous())
+                elif what == "gamma_bias":
+                    value = (self.gamma_modifier.bias + self.gamma).contiguous()
+                elif self.gamma_mode == 'learnable':
+                    value = (self.gamma_modifier + self.gamma).to(dtype=dtype).expand(B, self.n_heads).contiguous()
+                else:
+                    value = torch.full((B, self.n_heads), float(self.gamma), dtype=dtype, device=device)
+            cache[what] = (key, value)
+            return value
+
         def forward_with_state(self, hidden_states, init_ram=None, mask=None, position_ids=None, t_dim=1, inplace=False):
             if not self._fused_step_ok(hidden_states, init_ram, t_dim, inplace):
                 return super().forward_with_state(hidden_states, init_ram=init_ram, mask=mask, position_ids=position_ids,
@@ -75,18 +100,20 @@ def fused_attention_class():
             r_addr = self.r_proj(h).view(B, H, U, P)
             w_addr = self.w_proj(h).view(B, H, U, P)
             values = self.v_proj(h).view(B, H, C)
-            if self.r_scale is not None:
-                r_addr = (torch.exp(self.r_scale) / self.addr_temperature).to(dtype=r_addr.dtype).unsqueeze(-1) * r_addr
-                w_addr = (torch.exp(self.w_scale) / self.addr_temperature).to(dtype=w_addr.dtype).unsqueeze(-1) * w_addr
+            r_mul = w_mul = None
+            if self.r_scale is not None:  # applied inside the kernel where it takes them, else by the operator
+                r_mul, w_mul = self._step_constants("scales", r_addr.dtype, h.device, B)
             else:
                 r_addr = r_addr / self.addr_temperature
                 w_addr = w_addr / self.addr_temperature
-            if self.gamma_mode == 'learnable':
-                gamma = (self.gamma_modifier + self.gamma).to(dtype=values.dtype).expand(B, H)
-            elif self.gamma_mode == 'dynamic':
-                gamma = self.gamma_modifier(h) + self.gamma
+            if self.gamma_mode == 'dynamic':
+                lin = self.gamma_modifier
+                if lin.bias is None or type(lin) is not torch.nn.Linear:
+                    gamma = lin(h) + self.gamma
+                else:  # the constant is folded into the bias: one GEMM, no separate add
+                    gamma = torch.nn.functional.linear(h, lin.weight, self._step_constants("gamma_bias", lin.bias.dtype, h.device, B))
             else:
-                gamma = torch.full((B, H), float(self.gamma), dtype=values.dtype, device=values.device)
+                gamma = self._step_constants("gamma", values.dtype, h.device, B)
             if position_ids is None:
                 position_ids = torch.zeros(B, 1, dtype=torch.long, device=h.device)
             pos = position_ids.reshape(B).to(torch.int32)
@@ -103,7 +130,7 @@ def fused_attention_class():
             y = torch.ops.ramnet_ops.decode_fused_(
                 w_addr.contiguous(), r_addr.contiguous(), values.contiguous(), gamma.contiguous().to(values.dtype), slot, mass,
                 step_mask, self.embed_num, pos, w_k, r_k, float(self.top_k_re_norm[0]), float(self.top_k_re_norm[1]),
-                bool(self.mass_aware), float(self.ram_attn_eps), norm_weight, gate_logits, norm_eps)
+                bool(self.mass_aware), float(self.ram_attn_eps), norm_weight, gate_logits, norm_eps, w_mul, r_mul)
             return self.o_proj(y.reshape(B, 1, H * C)), RAMState(slot, mass)
 
         def forward(self, hidden_states, attention_mask=None, past_key_values=None, use_cache=False,

@@ -102,3 +102,31 @@ def test_state_beyond_int32_offsets_is_rejected_or_supported_by_shape_checks():
                                                   x, torch.zeros(1, 1, device="cuda"), torch.zeros(1, 1, 15, 8, device="cuda"),
                                                   torch.zeros(1, 1, 15, device="cuda"), torch.empty(0, dtype=torch.bool, device="cuda"),
                                                   0, torch.zeros(1, dtype=torch.int32, device="cuda"), 2, 2, 0.0, 0.0, False, 1e-6)
+
+
+@pytest.mark.parametrize("B,H,U,P,C,K,dtype", [
+    (3, 7, 2, 64, 128, (16, 16), torch.bfloat16),   # scales applied inside the one-warp-per-pair kernel
+    (2, 4, 2, 64, 256, (16, 16), torch.float16),
+    (2, 4, 3, 8, 32, (8, 8), torch.bfloat16),        # no kernel support for this shape: the operator multiplies first
+    (2, 4, 2, 16, 64, (4, 4), torch.float32),
+])
+def test_logit_scales_equal_a_multiply_beforehand(B, H, U, P, C, K, dtype):
+    """decode_fused_ with (H,U) logit scales == the same step on logits multiplied beforehand in the logits'
+    dtype (what the attention layer does with its learned scale over the temperature): same bits."""
+    ops()
+    w, r, x, g, slot, mass, pos = _inputs(B, H, U, P, C, dtype, 40)
+    ws = (torch.rand(H, U, generator=torch.Generator().manual_seed(50)) * 1.5 + 0.25).to(dtype)
+    rs = (torch.rand(H, U, generator=torch.Generator().manual_seed(51)) * 1.5 + 0.25).to(dtype)
+    nomask = torch.empty(0, dtype=torch.bool, device="cuda")
+    results = []
+    for fold in (True, False):
+        s, m = slot.clone().cuda(), mass.clone().cuda()
+        wl, rl = w.cuda(), r.cuda()
+        if not fold:
+            wl, rl = ws.cuda().unsqueeze(-1) * wl, rs.cuda().unsqueeze(-1) * rl
+        y = torch.ops.ramnet_ops.decode_fused_(wl, rl, x.cuda(), g.cuda(), s, m, nomask, H // 2, pos.cuda(), K[0], K[1],
+                                               0.0, 0.5, False, 1e-6, None, None, 0.0,
+                                               ws.cuda() if fold else None, rs.cuda().unsqueeze(-1) if fold else None)
+        results.append((y.cpu(), s.cpu(), m.cpu()))
+    for name, a, b in zip(("y", "slot", "mass"), results[0], results[1]):
+        assert torch.equal(a, b), f"{name}: {int((a != b).sum())} elements differ"
