@@ -141,12 +141,15 @@ int rn_decode_step(const void *w_addr, const void *r_addr, const void *x, const 
  *                     round_to_dtype(factor * logit), exactly what the separate multiply produces.
  * Taken where rn_decode_scales_supported() returns 1 (16-bit logits, U=2, P=64, Kw=Kr=16, C in {128, 256});
  * elsewhere the call fails and the caller multiplies beforehand.
+ *  batch_strides    : NULL (all inputs contiguous) or 5 element strides between the batch rows of w_addr, r_addr,
+ *                     x, gamma and gate_logits; inside a batch row the heads are contiguous.  This lets the inputs
+ *                     be column slices of ONE projection output (the layer's five projections merged into one GEMM).
  */
 int rn_decode_scales_supported(int dtype, int64_t U, int64_t P, int64_t C, int64_t Kw, int64_t Kr);
 int rn_decode_step_scaled(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
                           float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
                           const float *norm_weight, const void *gate_logits, double norm_eps,
-                          const void *w_scale, const void *r_scale,
+                          const void *w_scale, const void *r_scale, const int64_t *batch_strides,
                           int64_t B, int64_t H, int64_t U, int64_t P, int64_t C, int64_t E,
                           int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
                           int mass_aware, double eps, int device, void *stream);

@@ -32,6 +32,9 @@ struct RnDecodeParams {
     const float *norm_weight;
     const void *gate;
     const void *scale[2];  // optional (H,U) factors of the write / read logits, in the dtype of the logits
+    // element strides between batch rows of w_addr / r_addr, x, gamma and the gate logits (heads are contiguous
+    // inside a batch row: the inputs may be column slices of one wider projection output)
+    int64_t ld_addr[2], ld_x, ld_gamma, ld_gate;
     float norm_eps;
     int B, H, U, P, C, E, A;
     int K[2];
@@ -40,6 +43,12 @@ struct RnDecodeParams {
     float eps;
     int *status;  // the device's status word (rn_status_word): set when a bounded wait runs out
 };
+
+// element offset of the (b,h) row of an input whose batch rows are `ld` apart and whose heads take `per_head` each
+__device__ __forceinline__ int64_t rn_in_row(const RnDecodeParams &p, const int bh, const int64_t ld, const int per_head) {
+    const int b = bh / p.H, h = bh - b * p.H;
+    return b * ld + int64_t(h) * per_head;
+}
 
 template <typename T, int KPL, int PPL>
 __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDecodeParams p) {
@@ -72,7 +81,7 @@ __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDe
 
     if (warp < 2) {
         RnDigitLoader<T> load;
-        load.base = static_cast<const T *>(warp == 0 ? p.w_addr : p.r_addr) + int64_t(bh) * p.U * p.P;
+        load.base = static_cast<const T *>(warp == 0 ? p.w_addr : p.r_addr) + rn_in_row(p, bh, p.ld_addr[warp == 0 ? 0 : 1], p.U * p.P);
         load.su = p.P;
         load.sp = 1;
         const int K = p.K[warp];
@@ -88,13 +97,13 @@ __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDe
             }
         }
     } else {
-        const T *x = static_cast<const T *>(p.x) + int64_t(bh) * C;
+        const T *x = static_cast<const T *>(p.x) + rn_in_row(p, bh, p.ld_x, C);
         for (int c = tid - 64; c < C; c += 64) xs[c] = rn_to_float<T>(x[c]);
     }
     for (int c = tid; c < RN_DEC_WARPS * C; c += blockDim.x) yred[c] = 0.f;
     __syncthreads();
 
-    const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[bh]);
+    const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[rn_in_row(p, bh, p.ld_gamma, 1)]);
     float *slot = p.slot + int64_t(bh) * p.A * C;
     float *mass = p.mass + int64_t(bh) * p.A;
     const bool vec4 = (C & 3) == 0;
@@ -196,7 +205,7 @@ __global__ void __launch_bounds__(RN_DEC_WARPS * 32) rn_decode_kernel(const RnDe
         __syncthreads();
         inv_rms = bcast;
     }
-    const T *gate = p.gate ? static_cast<const T *>(p.gate) + int64_t(bh) * C : nullptr;
+    const T *gate = p.gate ? static_cast<const T *>(p.gate) + rn_in_row(p, bh, p.ld_gate, C) : nullptr;
     for (int c = tid; c < C; c += blockDim.x) {
         float v = yred[c];
         if (p.norm_weight != nullptr) v = v * inv_rms * p.norm_weight[c];
@@ -244,7 +253,7 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
         const int pair = group & 15, which = group >> 4;
         const int bh = min(bh0 + pair, BH - 1);  // surplus groups redo the last pair and discard it
         const int b = bh / p.H, h = bh % p.H;
-        const T *src = static_cast<const T *>(which ? p.r_addr : p.w_addr) + int64_t(bh) * U * P;
+        const T *src = static_cast<const T *>(which ? p.r_addr : p.w_addr) + rn_in_row(p, bh, p.ld_addr[which ? 1 : 0], U * P);
         int content[K];
         float weight[K];
         rn_fast::quad_decode<T, U, P, K>(src, p.re_norm[which], gl, content, weight);
@@ -274,10 +283,10 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
         }
         float *slot = p.slot + int64_t(bh) * p.A * C;
         float *mass = p.mass + int64_t(bh) * p.A;
-        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[bh]);
+        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[rn_in_row(p, bh, p.ld_gamma, 1)]);
         float4 xv[NV];
 #pragma unroll
-        for (int v = 0; v < NV; ++v) xv[v] = rn_load4<T>(static_cast<const T *>(p.x) + int64_t(bh) * C + v * 128 + lane * 4);
+        for (int v = 0; v < NV; ++v) xv[v] = rn_load4<T>(static_cast<const T *>(p.x) + rn_in_row(p, bh, p.ld_x, C) + v * 128 + lane * 4);
 
         // ---- write rows: bulk copies into this warp's buffer -------------------------------------------
         const int a_l = lane < K ? sel_slot[pair][0][lane] : 0;
@@ -404,7 +413,7 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
         if (p.gate != nullptr) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) {
-                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + int64_t(bh) * C + v * 128 + lane * 4);
+                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + rn_in_row(p, bh, p.ld_gate, C) + v * 128 + lane * 4);
                 acc[v].x /= 1.f + expf(-gl.x); acc[v].y /= 1.f + expf(-gl.y);
                 acc[v].z /= 1.f + expf(-gl.z); acc[v].w /= 1.f + expf(-gl.w);
             }
@@ -464,7 +473,7 @@ __global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kern
 
     const T *logit_base = static_cast<const T *>(which ? p.r_addr : p.w_addr);
     uint2 logits[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-    if (first + warp < last) rn_half::load_logits<T>(logit_base + int64_t(first + warp) * U * P, lane, logits);
+    if (first + warp < last) rn_half::load_logits<T>(logit_base + rn_in_row(p, first + warp, p.ld_addr[which], U * P), lane, logits);
 #pragma unroll 1
     for (int bh = first + warp; bh < last;) {
         int following = 0;
@@ -472,7 +481,7 @@ __global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kern
         following = __shfl_sync(RN_FULL, following, 0);
         // the logits of the following pair are requested now and used after this pair is done
         uint2 logits_next[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-        if (following < last) rn_half::load_logits<T>(logit_base + int64_t(following) * U * P, lane, logits_next);
+        if (following < last) rn_half::load_logits<T>(logit_base + rn_in_row(p, following, p.ld_addr[which], U * P), lane, logits_next);
         phase = rn_decode_pair_task<T, NV>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
         if (phase & 2u) {  // a bulk copy never completed: the pair this warp had already drawn gets a zero output
             if (following < last) {
@@ -508,11 +517,11 @@ __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p,
         float *mass = p.mass + int64_t(bh) * p.A;
 
         // inputs that do not depend on the addresses are requested first
-        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[bh]);
+        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[rn_in_row(p, bh, p.ld_gamma, 1)]);
         const int shift = (h < p.E) ? rn_pos_mod(p.pos[b], p.A) : 0;
         RnRaw4<T> xraw[NV];
 #pragma unroll
-        for (int v = 0; v < NV; ++v) xraw[v] = rn_load_raw4<T>(static_cast<const T *>(p.x) + int64_t(bh) * C + v * 128 + lane * 4);
+        for (int v = 0; v < NV; ++v) xraw[v] = rn_load_raw4<T>(static_cast<const T *>(p.x) + rn_in_row(p, bh, p.ld_x, C) + v * 128 + lane * 4);
 
         // ---- both addresses of the pair --------------------------------------------------------------
         int content;
@@ -694,7 +703,7 @@ __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p,
         if (p.gate != nullptr) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) {
-                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + int64_t(bh) * C + v * 128 + lane * 4);
+                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + rn_in_row(p, bh, p.ld_gate, C) + v * 128 + lane * 4);
                 acc[v].x /= 1.f + expf(-gl.x); acc[v].y /= 1.f + expf(-gl.y);
                 acc[v].z /= 1.f + expf(-gl.z); acc[v].w /= 1.f + expf(-gl.w);
             }
@@ -764,6 +773,7 @@ static int rn_launch_decode_fast(const RnDecodeParams &p, int device, cudaStream
                          reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y) |
                          reinterpret_cast<uintptr_t>(p.gate) | reinterpret_cast<uintptr_t>(p.norm_weight);
     if ((io & 15) != 0 || (size_t(p.U) * p.P * esz) % 16 != 0) return -1;
+    if (((p.ld_addr[0] | p.ld_addr[1] | p.ld_x | p.ld_gate) * int64_t(esz)) % 16 != 0) return -1;
     if (rn_launch_decode_pair<T>(p, device, stream) == 0) return 0;
     if (p.U == 2 && p.P == 64 && p.K[0] == 16) return rn_launch_decode_fast_c<T, 2, 64, 16>(p, stream);
     if (p.U == 3 && p.P == 32 && p.K[0] == 8) return rn_launch_decode_fast_c<T, 3, 32, 8>(p, stream);
@@ -790,9 +800,9 @@ static int rn_launch_decode(const RnDecodeParams &p, int kpl, int ppl, int grid,
 extern "C" int rn_decode_step_scaled(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
                                      float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
                                      const float *norm_weight, const void *gate_logits, double norm_eps,
-                                     const void *w_scale, const void *r_scale, int64_t B, int64_t H, int64_t U, int64_t P,
-                                     int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
-                                     int mass_aware, double eps, int device, void *stream);
+                                     const void *w_scale, const void *r_scale, const int64_t *batch_strides, int64_t B,
+                                     int64_t H, int64_t U, int64_t P, int64_t C, int64_t E, int64_t Kw, int64_t Kr,
+                                     double w_re_norm, double r_re_norm, int mass_aware, double eps, int device, void *stream);
 
 // 1 when rn_decode_step_scaled() takes logit scales for this shape (the one-warp-per-pair kernel does), else 0
 extern "C" int rn_decode_scales_supported(int dtype, int64_t U, int64_t P, int64_t C, int64_t Kw, int64_t Kr) {
@@ -805,15 +815,16 @@ extern "C" int rn_decode_step(const void *w_addr, const void *r_addr, const void
                               int64_t U, int64_t P, int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm,
                               double r_re_norm, int mass_aware, double eps, int device, void *stream) {
     return rn_decode_step_scaled(w_addr, r_addr, x, gamma, dtype, slot, mass, mask, pos, y, norm_weight, gate_logits, norm_eps,
-                                 nullptr, nullptr, B, H, U, P, C, E, Kw, Kr, w_re_norm, r_re_norm, mass_aware, eps, device, stream);
+                                 nullptr, nullptr, nullptr, B, H, U, P, C, E, Kw, Kr, w_re_norm, r_re_norm, mass_aware, eps, device,
+                                 stream);
 }
 
 extern "C" int rn_decode_step_scaled(const void *w_addr, const void *r_addr, const void *x, const void *gamma, int dtype,
                                      float *slot, float *mass, const uint8_t *mask, const int32_t *pos, void *y,
                                      const float *norm_weight, const void *gate_logits, double norm_eps,
-                                     const void *w_scale, const void *r_scale, int64_t B, int64_t H, int64_t U, int64_t P,
-                                     int64_t C, int64_t E, int64_t Kw, int64_t Kr, double w_re_norm, double r_re_norm,
-                                     int mass_aware, double eps, int device, void *stream) {
+                                     const void *w_scale, const void *r_scale, const int64_t *batch_strides, int64_t B,
+                                     int64_t H, int64_t U, int64_t P, int64_t C, int64_t E, int64_t Kw, int64_t Kr,
+                                     double w_re_norm, double r_re_norm, int mass_aware, double eps, int device, void *stream) {
     rn_clear_error();
     RN_REQUIRE((w_scale == nullptr) == (r_scale == nullptr), "give both logit scales or none");
     RN_REQUIRE(w_scale == nullptr || rn_decode_scales_supported(dtype, U, P, C, Kw, Kr),
@@ -844,6 +855,13 @@ extern "C" int rn_decode_step_scaled(const void *w_addr, const void *r_addr, con
     p.slot = slot; p.mass = mass; p.mask = mask; p.pos = pos; p.y = y;
     p.norm_weight = norm_weight; p.gate = gate_logits; p.norm_eps = float(norm_eps);
     p.scale[0] = w_scale; p.scale[1] = r_scale;
+    p.ld_addr[0] = batch_strides ? batch_strides[0] : H * U * P;
+    p.ld_addr[1] = batch_strides ? batch_strides[1] : H * U * P;
+    p.ld_x = batch_strides ? batch_strides[2] : H * C;
+    p.ld_gamma = batch_strides ? batch_strides[3] : H;
+    p.ld_gate = batch_strides ? batch_strides[4] : H * C;
+    RN_REQUIRE(p.ld_addr[0] >= H * U * P && p.ld_addr[1] >= H * U * P && p.ld_x >= H * C && p.ld_gamma >= H && p.ld_gate >= H * C,
+               "a batch stride is smaller than a batch row");
     p.B = int(B); p.H = int(H); p.U = int(U); p.P = int(P); p.C = int(C); p.E = int(E); p.A = int(A);
     p.K[0] = int(Kw); p.K[1] = int(Kr);
     p.re_norm[0] = float(w_re_norm); p.re_norm[1] = float(r_re_norm);

@@ -39,7 +39,7 @@ lib.rn_decode_step.restype = ctypes.c_int
 lib.rn_decode_step.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _f64,
                                _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f64, _f64, _i32, _f64, _i32, _ptr]
 lib.rn_decode_step_scaled.restype = ctypes.c_int
-lib.rn_decode_step_scaled.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _f64, _ptr, _ptr,
+lib.rn_decode_step_scaled.argtypes = [_ptr, _ptr, _ptr, _ptr, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _f64, _ptr, _ptr, _i64p,
                                       _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f64, _f64, _i32, _f64, _i32, _ptr]
 lib.rn_decode_scales_supported.restype = ctypes.c_int
 lib.rn_decode_scales_supported.argtypes = [_i32, _i64, _i64, _i64, _i64, _i64]

@@ -8,6 +8,8 @@ pointers, sizes and strides to the C ABI; nothing here computes on the CPU.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _C
@@ -205,6 +207,14 @@ def _topk_addr_backward(idx, val, w_addr, r_addr, D_val, embed_num, position_ids
 # ----------------------------------------------------------------------------------------------
 # fused decode step
 # ----------------------------------------------------------------------------------------------
+def _batch_rows(t: torch.Tensor) -> torch.Tensor:
+    """A decode input as the kernels take it: every batch row one contiguous block (heads and what follows them
+    contiguous), any stride between the batch rows: a column slice of a wider projection output needs no copy."""
+    if t.dim() >= 2 and t.size(0) > 0 and t[0].is_contiguous() and (t.size(0) == 1 or t.stride(0) >= t[0].numel()):
+        return t
+    return t.contiguous()
+
+
 def decode_scales_supported(dtype, U, P, C, w_top_k, r_top_k) -> bool:
     from ._C import DTYPE_CODE
     code = DTYPE_CODE.get(dtype)
@@ -232,7 +242,7 @@ def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_
         if not decode_scales_supported(w_addr.dtype, U, P, C, w_top_k, r_top_k):
             w_addr, r_addr = w_scale.unsqueeze(-1) * w_addr, r_scale.unsqueeze(-1) * r_addr
             w_scale = r_scale = None
-    w_addr, r_addr, x, gamma = (t.contiguous() for t in (w_addr, r_addr, x, gamma))
+    w_addr, r_addr, x, gamma = (_batch_rows(t) for t in (w_addr, r_addr, x, gamma))
     if not (r_addr.dtype == x.dtype == gamma.dtype == w_addr.dtype):
         raise RuntimeError("w_addr, r_addr, x and gamma must share one dtype")
     pos = _int32(position_ids).contiguous()
@@ -242,13 +252,15 @@ def decode_impl(w_addr, r_addr, x, gamma, slot, mass, mask, embed_num, position_
     if norm_weight is not None:
         norm_weight = norm_weight.to(torch.float32).contiguous()
     if gate_logits is not None:
-        gate_logits = gate_logits.to(x.dtype).contiguous()
-    y = torch.empty_like(x)
+        gate_logits = _batch_rows(gate_logits.to(x.dtype))
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     if y.numel() == 0:
         return y
+    batch_strides = (ctypes.c_int64 * 5)(w_addr.stride(0), r_addr.stride(0), x.stride(0), gamma.stride(0),
+                                         H * C if gate_logits is None else gate_logits.stride(0))
     check(lib.rn_decode_step_scaled(ptr(w_addr), ptr(r_addr), ptr(x), ptr(gamma), dtype_code(x), ptr(slot), ptr(mass),
                                     ptr(mask_u8), ptr(pos), ptr(y), ptr(norm_weight), ptr(gate_logits), float(norm_eps),
-                                    ptr(w_scale), ptr(r_scale), B, H, U, P, C, embed_num, w_top_k, r_top_k,
+                                    ptr(w_scale), ptr(r_scale), batch_strides, B, H, U, P, C, embed_num, w_top_k, r_top_k,
                                     float(w_re_norm), float(r_re_norm), int(mass_aware), float(eps), x.device.index,
                                     stream_of(x)))
     check_device(y)

@@ -88,6 +88,58 @@ def fused_attention_class():
             cache[what] = (key, value)
             return value
 
+        def _merged_projection(self, h):
+            """(r_addr (B,H,U,P), w_addr, values (B,H,C), gate logits or None, dynamic gamma (B,H) or None) from one
+            GEMM over the concatenated projection weights, or None when the modules are not plain ``Linear``.  The
+            concatenation is kept until a weight or bias changes."""
+            H, U, P, C = self.n_heads, self.addr_order, self.addr_radix, self.value_chs
+            mods = [self.r_proj, self.w_proj, self.v_proj]
+            if self.o_gate is not None:
+                mods.append(self.o_gate[0])
+            dyn = self.gamma_mode == 'dynamic'
+            if dyn:
+                mods.append(self.gamma_modifier)
+            if any(type(m) is not torch.nn.Linear for m in mods):
+                return None
+            tensors = [t for m in mods for t in (m.weight, m.bias) if t is not None]
+            key = (h.dtype, h.device, float(self.gamma), tuple((t.data_ptr(), t._version) for t in tensors))
+            cache = self.__dict__.setdefault("_rn_step_cache", {})
+            hit = cache.get("merged")
+            if hit is None or hit[0] != key:
+                with torch.no_grad():
+                    weight = torch.cat([m.weight for m in mods], dim=0).to(h.dtype)
+                    # rows of the output a multiple of 16 bytes apart (zero rows appended), so that the column slices
+                    # keep the alignment the vectorised decode kernels ask for
+                    pad = (-weight.size(0)) % 8
+                    if pad:
+                        weight = torch.cat([weight, weight.new_zeros(pad, weight.size(1))], dim=0)
+                    weight = weight.contiguous()
+                    bias = None
+                    if any(m.bias is not None for m in mods):
+                        parts = [m.bias if m.bias is not None else m.weight.new_zeros(m.weight.shape[0]) for m in mods]
+                        if dyn:  # the constant gamma rides on the bias of the gamma projection
+                            parts[-1] = parts[-1] + self.gamma
+                        if pad:
+                            parts.append(parts[0].new_zeros(pad))
+                        bias = torch.cat(parts).to(h.dtype).contiguous()
+                    elif dyn and float(self.gamma) != 0.0:
+                        return None
+                hit = (key, (weight, bias))
+                cache["merged"] = hit
+            weight, bias = hit[1]
+            z = torch.nn.functional.linear(h, weight, bias)
+            B, n = h.size(0), H * U * P
+            r_addr = z[:, :n].view(B, H, U, P)
+            w_addr = z[:, n:2 * n].view(B, H, U, P)
+            values = z[:, 2 * n:2 * n + H * C].view(B, H, C)
+            off = 2 * n + H * C
+            gate = None
+            if self.o_gate is not None:
+                gate = z[:, off:off + H * C].view(B, H, C)
+                off += H * C
+            gamma = z[:, off:off + H] if dyn else None
+            return r_addr, w_addr, values, gate, gamma
+
         def forward_with_state(self, hidden_states, init_ram=None, mask=None, position_ids=None, t_dim=1, inplace=False):
             if not self._fused_step_ok(hidden_states, init_ram, t_dim, inplace):
                 return super().forward_with_state(hidden_states, init_ram=init_ram, mask=mask, position_ids=position_ids,
@@ -96,17 +148,28 @@ def fused_attention_class():
             B = hidden_states.size(0)
             H, U, P, C = self.n_heads, self.addr_order, self.addr_radix, self.value_chs
             h = hidden_states[:, 0]
-            # projections, temperature and learned scale exactly as the parent class computes them
-            r_addr = self.r_proj(h).view(B, H, U, P)
-            w_addr = self.w_proj(h).view(B, H, U, P)
-            values = self.v_proj(h).view(B, H, C)
+            # The projections of the step (read / write logits, values, output gate, dynamic gamma) read the same
+            # input: one GEMM over their concatenated weights instead of five small ones.  At one token per
+            # sequence every GEMM is bound by reading its weights, and the small ones reach a fraction of the rate
+            # of the merged one.
+            merged = self._merged_projection(h)
+            if merged is None:
+                r_addr = self.r_proj(h).view(B, H, U, P)
+                w_addr = self.w_proj(h).view(B, H, U, P)
+                values = self.v_proj(h).view(B, H, C)
+                gate_logits = None if self.o_gate is None else self.o_gate[0](h).view(B, H, C)
+                gamma_dyn = None
+            else:
+                r_addr, w_addr, values, gate_logits, gamma_dyn = merged
             r_mul = w_mul = None
             if self.r_scale is not None:  # applied inside the kernel where it takes them, else by the operator
                 r_mul, w_mul = self._step_constants("scales", r_addr.dtype, h.device, B)
             else:
                 r_addr = r_addr / self.addr_temperature
                 w_addr = w_addr / self.addr_temperature
-            if self.gamma_mode == 'dynamic':
+            if self.gamma_mode == 'dynamic' and gamma_dyn is not None:
+                gamma = gamma_dyn
+            elif self.gamma_mode == 'dynamic':
                 lin = self.gamma_modifier
                 if lin.bias is None or type(lin) is not torch.nn.Linear:
                     gamma = lin(h) + self.gamma
@@ -125,10 +188,9 @@ def fused_attention_class():
                 # 16-bit inputs (not the epsilon of the input dtype); y is small, so which of the two is used matters
                 opmath = torch.float64 if values.dtype == torch.float64 else torch.float32
                 norm_eps = float(self.o_norm.eps) if self.o_norm.eps is not None else float(torch.finfo(opmath).eps)
-            gate_logits = None if self.o_gate is None else self.o_gate[0](h).view(B, H, C)
             w_k, r_k = _pair(self.top_k)
             y = torch.ops.ramnet_ops.decode_fused_(
-                w_addr.contiguous(), r_addr.contiguous(), values.contiguous(), gamma.contiguous().to(values.dtype), slot, mass,
+                w_addr, r_addr, values, gamma.to(values.dtype), slot, mass,
                 step_mask, self.embed_num, pos, w_k, r_k, float(self.top_k_re_norm[0]), float(self.top_k_re_norm[1]),
                 bool(self.mass_aware), float(self.ram_attn_eps), norm_weight, gate_logits, norm_eps, w_mul, r_mul)
             return self.o_proj(y.reshape(B, 1, H * C)), RAMState(slot, mass)

@@ -130,3 +130,43 @@ def test_logit_scales_equal_a_multiply_beforehand(B, H, U, P, C, K, dtype):
         results.append((y.cpu(), s.cpu(), m.cpu()))
     for name, a, b in zip(("y", "slot", "mass"), results[0], results[1]):
         assert torch.equal(a, b), f"{name}: {int((a != b).sum())} elements differ"
+
+
+@pytest.mark.parametrize("B,H,U,P,C,K,dtype", [
+    (3, 7, 2, 64, 128, (16, 16), torch.bfloat16),   # one warp per pair
+    (2, 4, 3, 32, 128, (8, 8), torch.float16),       # sixteen pairs per CTA
+    (2, 3, 2, 6, 10, (3, 5), torch.float32),         # general kernel
+])
+def test_inputs_may_be_column_slices_of_one_projection_output(B, H, U, P, C, K, dtype):
+    """The logits, values, gamma and gate logits of a step taken as column slices of ONE (B, N) matrix (the layer's
+    projections merged into one GEMM) give the same bits as contiguous copies of them."""
+    ops()
+    w, r, x, g, slot, mass, pos = _inputs(B, H, U, P, C, dtype, 60)
+    gate = randn((B, H, C), 66, dtype)
+    n = H * U * P
+    width = 8 + 2 * n + 2 * H * C + H
+    width += (-width) % 8 + 8              # rows a multiple of 16 bytes apart, so that the same kernel takes both forms
+    wide = torch.zeros(B, width, dtype=dtype)
+    cols = [(w, n), (r, n), (x, H * C), (gate, H * C), (g, H)]
+    off, views = 8, []                      # a leading pad: the slices do not start at the matrix's first column
+    for tns, width in cols:
+        wide[:, off:off + width] = tns.reshape(B, width)
+        views.append((off, width))
+        off += width
+    wide = wide.cuda()
+    shapes = [(B, H, U, P), (B, H, U, P), (B, H, C), (B, H, C), (B, H)]
+    nomask = torch.empty(0, dtype=torch.bool, device="cuda")
+    norm_w = (torch.rand(C, generator=torch.Generator().manual_seed(67)) + 0.5).cuda()
+    results = []
+    for sliced in (True, False):
+        ins = [wide[:, o:o + wd].view(shp) for (o, wd), shp in zip(views, shapes)]
+        if not sliced:
+            ins = [v.contiguous() for v in ins]
+        else:
+            assert not ins[0].is_contiguous()
+        s, m = slot.clone().cuda(), mass.clone().cuda()
+        y = torch.ops.ramnet_ops.decode_fused_(ins[0], ins[1], ins[2], ins[4], s, m, nomask, H // 2, pos.cuda(), K[0], K[1],
+                                               0.0, 0.0, False, 1e-6, norm_w, ins[3], 1e-6)
+        results.append((y.cpu(), s.cpu(), m.cpu()))
+    for name, a, b in zip(("y", "slot", "mass"), results[0], results[1]):
+        assert torch.equal(a, b), f"{name}: {int((a != b).sum())} elements differ"
