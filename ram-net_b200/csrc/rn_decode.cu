@@ -46,6 +46,7 @@ struct RnDecodeParams {
 
 // element offset of the (b,h) row of an input whose batch rows are `ld` apart and whose heads take `per_head` each
 __device__ __forceinline__ int64_t rn_in_row(const RnDecodeParams &p, const int bh, const int64_t ld, const int per_head) {
+    if (ld == int64_t(p.H) * per_head) return int64_t(bh) * per_head;  // contiguous: no division on the way to the first load
     const int b = bh / p.H, h = bh - b * p.H;
     return b * ld + int64_t(h) * per_head;
 }
@@ -438,12 +439,13 @@ __global__ void __launch_bounds__(RN_DECF_THREADS, 2) rn_decode_fast_kernel(cons
 // one for each of the 27.7 (b,h) pairs an SM gets at batch 256 x 16 heads, and no pair waits for a second round.
 template <int NV> struct RnDecPair { static constexpr int THREADS = NV == 1 ? 448 : 256; };
 
-template <typename T, int NV>
+template <typename T, int NV, bool EXTRA>
 __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
                                                         const int which, const uint32_t cand, const uint2 (&logits)[2],
                                                         float *wbuf, uint64_t *bar, uint32_t phase);
 
-template <typename T, int NV>
+// EXTRA: logit scales and / or strided batch rows (the plain instance carries none of that)
+template <typename T, int NV, bool EXTRA>
 __global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kernel(const RnDecodeParams p) {
     constexpr int U = 2, P = 64, K = 16;
     constexpr int RN_DECP_THREADS = RnDecPair<NV>::THREADS;
@@ -473,7 +475,7 @@ __global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kern
 
     const T *logit_base = static_cast<const T *>(which ? p.r_addr : p.w_addr);
     uint2 logits[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-    if (first + warp < last) rn_half::load_logits<T>(logit_base + rn_in_row(p, first + warp, p.ld_addr[which], U * P), lane, logits);
+    if (first + warp < last) rn_half::load_logits<T>(logit_base + (EXTRA ? rn_in_row(p, first + warp, p.ld_addr[which], U * P) : int64_t(first + warp) * (U * P)), lane, logits);
 #pragma unroll 1
     for (int bh = first + warp; bh < last;) {
         int following = 0;
@@ -481,8 +483,8 @@ __global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kern
         following = __shfl_sync(RN_FULL, following, 0);
         // the logits of the following pair are requested now and used after this pair is done
         uint2 logits_next[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-        if (following < last) rn_half::load_logits<T>(logit_base + rn_in_row(p, following, p.ld_addr[which], U * P), lane, logits_next);
-        phase = rn_decode_pair_task<T, NV>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
+        if (following < last) rn_half::load_logits<T>(logit_base + (EXTRA ? rn_in_row(p, following, p.ld_addr[which], U * P) : int64_t(following) * (U * P)), lane, logits_next);
+        phase = rn_decode_pair_task<T, NV, EXTRA>(p, bh, lane, hl, which, cand, logits, wbuf, &mbar[warp], phase);
         if (phase & 2u) {  // a bulk copy never completed: the pair this warp had already drawn gets a zero output
             if (following < last) {
                 T *yr = static_cast<T *>(p.y) + int64_t(following) * (NV * 128);
@@ -498,7 +500,7 @@ __global__ void __launch_bounds__(RnDecPair<NV>::THREADS, 2) rn_decode_pair_kern
 }
 
 // One (b,h) pair on one warp; phase bit 0 = parity of the warp's mbarrier, bit 1 = failure (returned).
-template <typename T, int NV>
+template <typename T, int NV, bool EXTRA>
 __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p, const int bh, const int lane, const int hl,
                                                         const int which, const uint32_t cand, const uint2 (&logits)[2],
                                                         float *wbuf, uint64_t *bar, uint32_t phase) {
@@ -517,17 +519,17 @@ __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p,
         float *mass = p.mass + int64_t(bh) * p.A;
 
         // inputs that do not depend on the addresses are requested first
-        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[rn_in_row(p, bh, p.ld_gamma, 1)]);
+        const float gamma = rn_to_float<T>(static_cast<const T *>(p.gamma)[(EXTRA ? rn_in_row(p, bh, p.ld_gamma, 1) : int64_t(bh) * (1))]);
         const int shift = (h < p.E) ? rn_pos_mod(p.pos[b], p.A) : 0;
         RnRaw4<T> xraw[NV];
 #pragma unroll
-        for (int v = 0; v < NV; ++v) xraw[v] = rn_load_raw4<T>(static_cast<const T *>(p.x) + rn_in_row(p, bh, p.ld_x, C) + v * 128 + lane * 4);
+        for (int v = 0; v < NV; ++v) xraw[v] = rn_load_raw4<T>(static_cast<const T *>(p.x) + (EXTRA ? rn_in_row(p, bh, p.ld_x, C) : int64_t(bh) * (C)) + v * 128 + lane * 4);
 
         // ---- both addresses of the pair --------------------------------------------------------------
         int content;
         float weight;
         uint2 scaled[2] = {logits[0], logits[1]};
-        if (p.scale[which] != nullptr) {
+        if (EXTRA && p.scale[which] != nullptr) {
             // the layer's learned scale over the temperature, one factor per (head, digit): the product is rounded
             // to the dtype of the logits, as the separate elementwise multiply of the layer code rounds it
             const T *sc = static_cast<const T *>(p.scale[which]) + h * U;
@@ -703,7 +705,7 @@ __device__ __forceinline__ uint32_t rn_decode_pair_task(const RnDecodeParams &p,
         if (p.gate != nullptr) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) {
-                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + rn_in_row(p, bh, p.ld_gate, C) + v * 128 + lane * 4);
+                const float4 gl = rn_load4<T>(static_cast<const T *>(p.gate) + (EXTRA ? rn_in_row(p, bh, p.ld_gate, C) : int64_t(bh) * (C)) + v * 128 + lane * 4);
                 acc[v].x /= 1.f + expf(-gl.x); acc[v].y /= 1.f + expf(-gl.y);
                 acc[v].z /= 1.f + expf(-gl.z); acc[v].w /= 1.f + expf(-gl.w);
             }
@@ -724,6 +726,8 @@ static int rn_launch_decode_pair(const RnDecodeParams &p, int device, cudaStream
         if (!(p.U == 2 && p.P == 64 && p.K[0] == 16 && p.K[1] == 16)) return -1;
         if (p.C != 128 && p.C != 256) return -1;
         const int threads = p.C == 128 ? RnDecPair<1>::THREADS : RnDecPair<2>::THREADS;
+        const bool extra = p.scale[0] != nullptr || p.ld_addr[0] != int64_t(p.H) * p.U * p.P || p.ld_addr[1] != int64_t(p.H) * p.U * p.P ||
+                           p.ld_x != int64_t(p.H) * p.C || p.ld_gamma != p.H || (p.gate != nullptr && p.ld_gate != int64_t(p.H) * p.C);
         const int wpc = threads / 32;
         // CTAs: enough for one warp per pair, but at least one per SM while there are pairs to hand out (a small
         // batch is spread over all SMs instead of filling a few), at most the two resident CTAs per SM
@@ -733,12 +737,22 @@ static int rn_launch_decode_pair(const RnDecodeParams &p, int device, cudaStream
         if (grid > 2 * sms) grid = 2 * sms;
         if (p.C == 128) {
             constexpr int smem = (RnDecPair<1>::THREADS / 32) * 16 * 128 * 4;
-            if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
-            rn_decode_pair_kernel<T, 1><<<grid, threads, smem, stream>>>(p);
+            if (extra) {
+                if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+                rn_decode_pair_kernel<T, 1, true><<<grid, threads, smem, stream>>>(p);
+            } else {
+                if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+                rn_decode_pair_kernel<T, 1, false><<<grid, threads, smem, stream>>>(p);
+            }
         } else {
             constexpr int smem = (RnDecPair<2>::THREADS / 32) * 16 * 256 * 4;
-            if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
-            rn_decode_pair_kernel<T, 2><<<grid, threads, smem, stream>>>(p);
+            if (extra) {
+                if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+                rn_decode_pair_kernel<T, 2, true><<<grid, threads, smem, stream>>>(p);
+            } else {
+                if (cudaFuncSetAttribute(rn_decode_pair_kernel<T, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -1;
+                rn_decode_pair_kernel<T, 2, false><<<grid, threads, smem, stream>>>(p);
+            }
         }
         return 0;
     }

@@ -210,8 +210,15 @@ def _topk_addr_backward(idx, val, w_addr, r_addr, D_val, embed_num, position_ids
 def _batch_rows(t: torch.Tensor) -> torch.Tensor:
     """A decode input as the kernels take it: every batch row one contiguous block (heads and what follows them
     contiguous), any stride between the batch rows: a column slice of a wider projection output needs no copy."""
-    if t.dim() >= 2 and t.size(0) > 0 and t[0].is_contiguous() and (t.size(0) == 1 or t.stride(0) >= t[0].numel()):
+    if t.is_contiguous():
         return t
+    if t.dim() >= 2:
+        inner, ok = 1, True
+        for size, stride in zip(reversed(t.shape[1:]), reversed(t.stride()[1:])):
+            ok = ok and (size == 1 or stride == inner)
+            inner *= size
+        if ok and t.stride(0) >= inner:
+            return t
     return t.contiguous()
 
 
