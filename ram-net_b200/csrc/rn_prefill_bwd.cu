@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
     auto wr_of = [&](int j) { return MODEL ? (j < 2) : (q + j * KL < Kw); };
     const unsigned gmask = (G >= 32 ? 0xffffffffu : ((1u << G) - 1u)) << (lane & ~(G - 1));  // the lanes of one event
 
-    // dynamic smem: rec[2][rec_stride] | S[A*CS] | xt[L*CS] (replay) | dyt[L*CS] | dxlate[L*Kw*CS] (reverse)
+    // dynamic smem: rec[2][rec_stride] | S[A*CS] | xt[L*CS] (replay) | dyt[L*CS] | per-(token,k) rows handed from the chains
+    // to the token's owners: dxlate[L*Kw*CS] (reverse: d_x parts of chain writes) or [L*Kr*CS] (replay: slot rows at chain reads)
     const size_t rec_stride = (size_t(rec_copy) + 127) / 128 * 128;
     unsigned char *rec0 = dyn;
     float *S = reinterpret_cast<float *>(dyn + 2 * rec_stride);  // slot slice (replay) or d_slot slice (reverse)
@@ -168,7 +169,10 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
             *reinterpret_cast<float4 *>(dyt + tok * CS + sub * 4) = dyv;
         }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // reverse: d_x of this token
-        uint32_t late = 0;                             // reverse: this thread's writes that a chain handles
+        uint32_t late = 0;                             // this thread's events that a chain handles (reverse: writes, replay: reads)
+        float late_cf[EV];                             // reverse: their coefficients (the record buffer may be refilled by then)
+#pragma unroll
+        for (int j = 0; j < EV; ++j) late_cf[j] = 0.f;
 
         // ---- token-major events: records, then rows (and deltas), then arithmetic, then stores --------------
         constexpr int NB = EV < 2 ? EV : 2;
@@ -191,7 +195,10 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                     row[i] = *reinterpret_cast<const float4 *>(S + (pr[i].y & 0xffffu) * CS + sub * 4);
                     if (REVERSE && wr_of(jb + i) && chan_ok) dl[i] = *reinterpret_cast<const float4 *>(dtok + k * CS);
                 } else if (kind <= RN_KIND_LATER) {
-                    if (REVERSE && wr_of(jb + i)) late |= 1u << (jb + i);
+                    if (wr_of(jb + i) == REVERSE) {  // reverse: writes, replay: reads that a chain handles
+                        late |= 1u << (jb + i);
+                        late_cf[jb + i] = __uint_as_float(pr[i].x);
+                    }
                 } else if (tok_ok && (MODEL || k < KT) && sub == 0 && wr_of(jb + i) == REVERSE) {
                     pchunk[tok * KT + k] = 0.f;  // a no-op event
                 }
@@ -250,23 +257,13 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                 uint2 pr = e_pair[e];
                 float *row = S + (pr.y & 0xffffu) * CS + csub * 4;
                 float4 s = *reinterpret_cast<float4 *>(row);
-                int ct = int(__umulhi(uint32_t(e), kt_magic)), ck = e - ct * KT;
-                float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (REVERSE && ck < Kw && cok) dl = *reinterpret_cast<const float4 *>(dchunk + (ct * Kw + ck) * CS + csub * 4);
                 for (int guard = 0; guard < RN_GSU_NE_MAX; ++guard) {
-                    // the following event's record (and delta) is requested before this one is applied
+                    // the following event's record is requested before this one is applied
                     const bool more_ev = (pr.y & RN_LINK_NEXT) != 0;
                     const int en = int((pr.y >> 16) & 0xfffu);
                     uint2 pr_n = make_uint2(0u, 0u);
-                    int ct_n = 0, ck_n = 0;
-                    float4 dl_n = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (more_ev) {
-                        pr_n = e_pair[en];
-                        ct_n = int(__umulhi(uint32_t(en), kt_magic));
-                        ck_n = en - ct_n * KT;
-                        if (REVERSE && ck_n < Kw && cok)
-                            dl_n = *reinterpret_cast<const float4 *>(dchunk + (ct_n * Kw + ck_n) * CS + csub * 4);
-                    }
+                    if (more_ev) pr_n = e_pair[en];
+                    const int ct = int(__umulhi(uint32_t(e), kt_magic)), ck = e - ct * KT;
                     const float cf = __uint_as_float(pr.x);
                     const bool wr = ck < Kw;
                     if (!REVERSE) {
@@ -279,18 +276,15 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                             s.z = fmaf(cf, d.z, s.z);
                             s.w = fmaf(cf, d.w, s.w);
                         }
-                        // the lanes of a group walk the same chain, so they are converged for this shuffle
-                        const float4 dyr = *reinterpret_cast<const float4 *>(dyt + ct * CS + csub * 4);
-                        float dot = wr ? 0.f : s.x * dyr.x + s.y * dyr.y + s.z * dyr.z + s.w * dyr.w;
-                        dot = rn_group_sum(dot, G, gmask);
-                        if (!wr && csub == 0) pchunk[ct * KT + ck] = dot;
+                        // a read hands the row as it is now to the token's owners, who take the dot product with d_y
+                        // after the chains (all threads at once, instead of one by one on the chain)
+                        if (!wr) *reinterpret_cast<float4 *>(dxlate + (ct * (KT - Kw) + (ck - Kw)) * CS + csub * 4) = s;
                     } else {
                         const float4 dyr = *reinterpret_cast<const float4 *>(dyt + ct * CS + csub * 4);
-                        float dot = wr ? s.x * dl.x + s.y * dl.y + s.z * dl.z + s.w * dl.w : 0.f;
-                        dot = rn_group_sum(dot, G, gmask);
                         if (wr) {
-                            if (csub == 0) pchunk[ct * KT + ck] = dot;
-                            *reinterpret_cast<float4 *>(dxlate + (ct * Kw + ck) * CS + csub * 4) = make_float4(cf * s.x, cf * s.y, cf * s.z, cf * s.w);
+                            // a write hands d_slot as it is now to the token's owners: they take the dot product with
+                            // the write's delta and the d_x part after the chains, all threads at once
+                            *reinterpret_cast<float4 *>(dxlate + (ct * Kw + ck) * CS + csub * 4) = s;
                             const float keep = 1.f - cf;
                             s.x *= keep; s.y *= keep; s.z *= keep; s.w *= keep;
                         } else {
@@ -303,9 +297,6 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
                     if (!more_ev) break;
                     e = en;
                     pr = pr_n;
-                    ct = ct_n;
-                    ck = ck_n;
-                    dl = dl_n;
                 }
                 *reinterpret_cast<float4 *>(row) = s;
             }
@@ -317,14 +308,39 @@ __global__ void __launch_bounds__(RN_APPLY_THREADS, 1) rn_gsu_bwd_sweep_kernel(c
             return;
         }
 
+        if (!REVERSE) {
+            // ---- d_r of the reads that a chain handled: <row at the read, d_y>, this slice's part -----------------
+#pragma unroll
+            for (int j = 0; j < EV; ++j) {
+                if (!(late & (1u << j))) continue;
+                const int k = q + j * KL;
+                const float4 v = *reinterpret_cast<const float4 *>(dxlate + (tok * (KT - Kw) + (k - Kw)) * CS + sub * 4);
+                const float4 dyr = *reinterpret_cast<const float4 *>(dyt + tok * CS + sub * 4);
+                float dot = v.x * dyr.x + v.y * dyr.y + v.z * dyr.z + v.w * dyr.w;
+                dot = rn_group_sum(dot, G, gmask);
+                if (sub == 0) pchunk[tok * KT + k] = dot;
+            }
+            // a token's threads share a warp: none of them goes on to overwrite the token's d_y row for the next chunk
+            // while another one still reads it here
+            __syncwarp();
+        }
         if (REVERSE) {
             // ---- d_x: the writes that a chain handled, then combine the k-lanes ----------------------------------
 #pragma unroll
             for (int j = 0; j < EV; ++j) {
                 if (!(late & (1u << j))) continue;
                 const int k = q + j * KL;
-                const float4 v = *reinterpret_cast<const float4 *>(dxlate + (tok * Kw + k) * CS + sub * 4);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                const float4 v = *reinterpret_cast<const float4 *>(dxlate + (tok * Kw + k) * CS + sub * 4);  // d_slot at the write
+                const float cf = late_cf[j];
+                float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (chan_ok) dl = *reinterpret_cast<const float4 *>(dtok + k * CS);
+                float dot = v.x * dl.x + v.y * dl.y + v.z * dl.z + v.w * dl.w;
+                dot = rn_group_sum(dot, G, gmask);
+                if (sub == 0) pchunk[tok * KT + k] = dot;
+                acc.x = fmaf(cf, v.x, acc.x);
+                acc.y = fmaf(cf, v.y, acc.y);
+                acc.z = fmaf(cf, v.z, acc.z);
+                acc.w = fmaf(cf, v.w, acc.w);
             }
             for (int off = G; off < TPT; off <<= 1) {
                 acc.x += __shfl_xor_sync(RN_FULL, acc.x, off);
@@ -622,7 +638,7 @@ static int rn_launch_sweep(const RnGsuBwdParams &bp, const RnGsuPlan &pl, cudaSt
     const int grid = bp.f.B * bp.f.H * pl.nslices;
     // records double buffered, state slice, x / d_y rows of the chunk, per-(token,k) d_x buffer of the reverse chains
     const size_t smem = 2 * rn_align(size_t(pl.NEp) * 9 + 16, 128) +
-                        (size_t(bp.f.A) * pl.cs + 2 * size_t(pl.L) * pl.cs + (REVERSE ? size_t(pl.L) * bp.f.Kw * pl.cs : 0)) * 4;
+                        (size_t(bp.f.A) * pl.cs + 2 * size_t(pl.L) * pl.cs + size_t(pl.L) * (REVERSE ? bp.f.Kw : bp.f.Kr) * pl.cs) * 4;
     if (smem > 227 * 1024) {
         rn_set_error("backward sweep needs %zu bytes of shared memory", smem);
         return 1;
